@@ -1,6 +1,7 @@
 """Cache manager: pages and block tables for every request, in every cache group.
 
-A *cache group* is a set of layers with the same need: all keys, or a window of them.  Every
+A *cache group* is a set of layers with the same need: all keys, a window of them, or the keys
+of the running chunk of positions.  Every
 group has a pool of pages of its own (its own allocator and its own device tensors) and every
 request has one block table per group.  All tables of a request have the same logical length,
 because every group caches the same token positions; they differ in what has been given back:
@@ -36,6 +37,9 @@ class CacheGroup:
     window: Optional[int] = None
     # Keys 0 .. keep_first - 1 are never passed by the window: their pages are kept.
     keep_first: int = 0
+    # A chunked mask instead of a window: a query sees the keys of its own chunk of ``chunk``
+    # positions (counted from 0), so whole pages before the running chunk are given back.
+    chunk: int = 0
 
 
 @dataclass
@@ -148,9 +152,13 @@ class CacheManager:
         """
         seq.num_computed += num_tokens
         for index, group in enumerate(self.groups):
-            if group.window is None:
+            if group.window is None and not group.chunk:
                 continue
-            first_needed = seq.num_computed - group.window + 1
+            if group.window is None:
+                # The next query, at position num_computed, sees its own chunk's keys only.
+                first_needed = seq.num_computed // group.chunk * group.chunk
+            else:
+                first_needed = seq.num_computed - group.window + 1
             if first_needed <= 0:
                 continue
             dead_blocks = min(first_needed // self.page_size, len(seq.tables[index]))

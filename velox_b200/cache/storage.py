@@ -25,10 +25,13 @@ class LayerCache:
     v: Optional[torch.Tensor] = None
     state: Optional[torch.Tensor] = None  # [max_num_seqs + 1, *shape]; last row is for padding
     read_only: bool = False              # the cache belongs to another schedule entry
+    # The block arrangement's own state rows, [max_num_seqs + 1, *shape]; every schedule entry has
+    # its own, also one that reads another entry's pages.
+    block_state: Optional[torch.Tensor] = None
 
     def num_bytes(self) -> int:
         total = 0
-        for t in (self.k, None if self.v is self.k else self.v, self.state):
+        for t in (self.k, None if self.v is self.k else self.v, self.state, self.block_state):
             if t is not None:
                 total += t.numel() * t.element_size()
         return total
@@ -52,7 +55,15 @@ def allocate_layer_cache(
         cache.state = torch.zeros(
             (max_num_seqs + 1,) + tuple(needs.state.shape), dtype=needs.state.dtype, device=device
         )
+    cache.block_state = allocate_block_state(needs, max_num_seqs, device)
     return cache
+
+
+def allocate_block_state(needs: CacheNeeds, max_num_seqs: int, device: torch.device) -> Optional[torch.Tensor]:
+    if needs.block_state is None:
+        return None
+    return torch.zeros((max_num_seqs + 1,) + tuple(needs.block_state.shape), dtype=needs.block_state.dtype,
+                       device=device)
 
 
 def bytes_per_page(needs_list: List[CacheNeeds], page_size: int, dtype: torch.dtype) -> int:

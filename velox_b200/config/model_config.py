@@ -615,6 +615,235 @@ class RedalixConfig(ModelConfig):
         return out
 
 
+@dataclass(frozen=True)
+class ScoredAttentionConfig:
+    """Causal softmax attention over all keys with grouped heads, no rotation, a term of score 0
+    in every denominator and a distance bias per head; ``q_temp`` (or None) = (coef, every): the
+    query at position p is multiplied by ``1 + coef * ln(floor((p + 1) / every) + 1)``."""
+
+    heads: int
+    kv_heads: int
+    dim: int
+    vdim: int
+    scale: float
+    q_temp: Optional[Tuple[float, int]] = None
+
+    @staticmethod
+    def parse(m: Mapping[str, Any], where: str) -> "ScoredAttentionConfig":
+        heads, kv_heads = _count(m, "heads", where), _count(m, "kv_heads", where)
+        if heads % kv_heads:
+            raise ConfigError(f"{where}: heads={heads} must be a multiple of kv_heads={kv_heads}")
+        for key in ("rot", "mask", "softcap", "diff"):
+            if m.get(key) is not None:
+                raise ConfigError(f"{where}: {key!r} is not a key of this mixer")
+        q_temp = None
+        if m.get("q_temp") is not None:
+            t = _mapping(m, "q_temp", where)
+            q_temp = (_number(t, "coef", where + ".q_temp"), _count(t, "every", where + ".q_temp"))
+        return ScoredAttentionConfig(heads=heads, kv_heads=kv_heads, dim=_count(m, "dim", where),
+                                     vdim=_count(m, "vdim", where), scale=_number(m, "scale", where), q_temp=q_temp)
+
+    def to_json_dict(self) -> Dict[str, Any]:
+        out: Dict[str, Any] = {"heads": self.heads, "kv_heads": self.kv_heads, "dim": self.dim, "vdim": self.vdim,
+                               "scale": self.scale}
+        if self.q_temp is not None:
+            out["q_temp"] = {"coef": self.q_temp[0], "every": self.q_temp[1]}
+        return out
+
+
+@dataclass(frozen=True)
+class DifferentialAttentionConfig:
+    """Two softmax maps per head over the same values, combined as ``a1 - lambda a2``.  ``rot``
+    (or None) = (base, dims); ``chunk`` (or None): the size of the chunks a query stays inside;
+    ``softcap`` (or None); ``diff``: the constant in lambda and in the output's factor."""
+
+    heads: int
+    kv_heads: int
+    dim: int
+    vdim: int
+    scale: float
+    diff: float
+    rot: Optional[Tuple[float, int]] = None
+    chunk: Optional[int] = None
+    softcap: Optional[float] = None
+
+    @staticmethod
+    def parse(m: Mapping[str, Any], where: str) -> "DifferentialAttentionConfig":
+        heads, kv_heads = _count(m, "heads", where), _count(m, "kv_heads", where)
+        if heads % kv_heads:
+            raise ConfigError(f"{where}: heads={heads} must be a multiple of kv_heads={kv_heads}")
+        dim = _count(m, "dim", where)
+        if m.get("q_temp") is not None:
+            raise ConfigError(f"{where}: 'q_temp' is not a key of this mixer")
+        rot = None
+        if m.get("rot") is not None:
+            r = _mapping(m, "rot", where)
+            dims = _count(r, "dims", where + ".rot")
+            if dims % 2 or dims > dim:
+                raise ConfigError(f"{where}.rot: dims={dims} must be even and at most dim={dim}")
+            base = _number(r, "base", where + ".rot")
+            if base <= 0:
+                raise ConfigError(f"{where}.rot: base={base} must be positive")
+            rot = (base, dims)
+        chunk = None
+        if m.get("mask") is not None:
+            mask = _mapping(m, "mask", where)
+            if mask.get("keep_first"):
+                raise ConfigError(f"{where}.mask: keep_first is not a key of this mixer")
+            chunk = _count(mask, "size", where + ".mask")
+        softcap = None
+        if m.get("softcap") is not None:
+            softcap = _number(m, "softcap", where)
+            if softcap <= 0:
+                raise ConfigError(f"{where}: softcap={softcap} must be positive")
+        return DifferentialAttentionConfig(
+            heads=heads, kv_heads=kv_heads, dim=dim, vdim=_count(m, "vdim", where), scale=_number(m, "scale", where),
+            diff=_number(m, "diff", where), rot=rot, chunk=chunk, softcap=softcap)
+
+    def to_json_dict(self) -> Dict[str, Any]:
+        out: Dict[str, Any] = {"heads": self.heads, "kv_heads": self.kv_heads, "dim": self.dim, "vdim": self.vdim,
+                               "scale": self.scale, "diff": self.diff}
+        if self.rot is not None:
+            out["rot"] = {"base": self.rot[0], "dims": self.rot[1]}
+        if self.chunk is not None:
+            out["mask"] = {"size": self.chunk}
+        if self.softcap is not None:
+            out["softcap"] = self.softcap
+        return out
+
+
+@dataclass(frozen=True)
+class ClampedFeedForwardConfig:
+    """A gated feed-forward of inner width ``ff`` whose gate and up values are clamped at
+    ``limit`` (None: no clamps)."""
+
+    ff: int
+    limit: Optional[float] = None
+
+    @staticmethod
+    def parse(m: Mapping[str, Any], where: str) -> "ClampedFeedForwardConfig":
+        kind = m.get("kind")
+        if kind != "dense":
+            raise ConfigError(f"{where}: mlp kind {kind!r} is not supported ('dense' is)")
+        limit = None
+        if m.get("limit") is not None:
+            limit = _number(m, "limit", where)
+            if limit <= 0:
+                raise ConfigError(f"{where}: limit={limit} must be positive")
+        return ClampedFeedForwardConfig(ff=_count(m, "ff", where), limit=limit)
+
+    def to_json_dict(self) -> Dict[str, Any]:
+        out: Dict[str, Any] = {"kind": "dense", "ff": self.ff}
+        if self.limit is not None:
+            out["limit"] = self.limit
+        return out
+
+
+@dataclass(frozen=True)
+class LizizenLayerConfig:
+    """``type`` attention: ``scored``; attention_2: ``differential``."""
+
+    type: str
+    scored: Optional[ScoredAttentionConfig] = None
+    differential: Optional[DifferentialAttentionConfig] = None
+    mlp: Optional[ClampedFeedForwardConfig] = None
+
+
+@dataclass(frozen=True)
+class LizizenConfig(ModelConfig):
+    """``Lizizen``: every layer is ``x <- x + mixer(shift(norm1(x))) + ff(norm2(x))`` with two RMS
+    norms of the same x whose weights are stored around zero, and a token shift in front of the
+    mixer; the mixer is ``attention`` (all keys, no rotation, query temperature, distance bias,
+    a term of score 0 in the denominator) or ``attention_2`` (two maps per head, query/key norm,
+    partial rotation, capped scores, chunked mask, an output gate); the feed-forward is gated
+    with clamps and biases.  ``loop`` = (start, stop, times): layers start .. stop - 1 run
+    ``times`` times in a row.  config.json keys: ``vocab``, ``width``, ``norm.eps``, ``layers``
+    (a list of ``{type, mixer, mlp}``) and ``loop``."""
+
+    layers: Tuple[LizizenLayerConfig, ...] = ()
+    loop: Optional[Tuple[int, int, int]] = None
+    norm_eps: float = 1e-6
+    torch_dtype: str = "bfloat16"
+
+    def run_order(self) -> Tuple[int, ...]:
+        """Layer indices in the order they run, a looped stretch repeated."""
+        n = len(self.layers)
+        if self.loop is None:
+            return tuple(range(n))
+        start, stop, times = self.loop
+        return tuple(range(start)) + tuple(range(start, stop)) * times + tuple(range(stop, n))
+
+    @staticmethod
+    def from_dict(cfg: Mapping[str, Any]) -> "LizizenConfig":
+        name = cfg.get("architecture") or (cfg.get("architectures") or ["Lizizen"])[0]
+        raw_layers = cfg.get("layers")
+        if not isinstance(raw_layers, (list, tuple)) or not raw_layers:
+            raise ConfigError("config.json key 'layers' must be a non-empty list")
+        layers = []
+        for index, raw in enumerate(raw_layers):
+            where = f"config.json layers[{index}]"
+            if not isinstance(raw, Mapping):
+                raise ConfigError(f"{where} must be an object")
+            kind = raw.get("type")
+            m = _mapping(raw, "mixer", where)
+            mlp = None
+            if raw.get("mlp") is not None:
+                mlp = ClampedFeedForwardConfig.parse(_mapping(raw, "mlp", where), where + ".mlp")
+            if kind == "attention":
+                layers.append(LizizenLayerConfig(type=kind, scored=ScoredAttentionConfig.parse(m, where + ".mixer"),
+                                                 mlp=mlp))
+            elif kind == "attention_2":
+                layers.append(LizizenLayerConfig(
+                    type=kind, differential=DifferentialAttentionConfig.parse(m, where + ".mixer"), mlp=mlp))
+            else:
+                raise ConfigError(f"{where}: layer type {kind!r} is not supported "
+                                  "('attention' and 'attention_2' are)")
+        loop = None
+        if cfg.get("loop") is not None:
+            lp = _mapping(cfg, "loop", "config.json")
+            start, stop = lp.get("start"), lp.get("stop")
+            for key, value in (("start", start), ("stop", stop)):
+                if isinstance(value, bool) or not isinstance(value, int) or value < 0:
+                    raise ConfigError(f"config.json loop: {key}={value!r} must be a non-negative integer")
+            times = _count(lp, "times", "config.json loop")
+            if not start <= stop <= len(layers):
+                raise ConfigError(f"config.json loop: start={start}, stop={stop} do not fit {len(layers)} layers")
+            loop = (start, stop, times)
+        eos = cfg.get("eos_token_id")
+        eos_ids: Tuple[int, ...] = () if eos is None else ((eos,) if isinstance(eos, int) else tuple(int(t) for t in eos))
+        return LizizenConfig(
+            architecture=str(name),
+            vocab_size=_count(cfg, "vocab", "config.json"),
+            hidden_size=_count(cfg, "width", "config.json"),
+            num_hidden_layers=len(layers),
+            max_position_embeddings=int(cfg.get("max_position_embeddings", 1 << 20)),
+            tie_word_embeddings=False,
+            eos_token_ids=eos_ids,
+            layers=tuple(layers),
+            loop=loop,
+            norm_eps=_number(_mapping(cfg, "norm", "config.json"), "eps", "config.json norm"),
+            torch_dtype=str(cfg.get("torch_dtype", "bfloat16")),
+        )
+
+    def to_json_dict(self) -> Dict[str, Any]:
+        layers = []
+        for layer in self.layers:
+            mixer = (layer.scored if layer.type == "attention" else layer.differential).to_json_dict()
+            layers.append({"type": layer.type, "mixer": mixer,
+                           "mlp": None if layer.mlp is None else layer.mlp.to_json_dict()})
+        out: Dict[str, Any] = {
+            "architecture": self.architecture, "vocab": self.vocab_size, "width": self.hidden_size,
+            "norm": {"eps": self.norm_eps}, "layers": layers, "torch_dtype": self.torch_dtype,
+        }
+        if self.loop is not None:
+            out["loop"] = dict(zip(("start", "stop", "times"), self.loop))
+        if self.max_position_embeddings != 1 << 20:
+            out["max_position_embeddings"] = self.max_position_embeddings
+        if self.eos_token_ids:
+            out["eos_token_id"] = list(self.eos_token_ids)
+        return out
+
+
 def read_config_json(model_dir: str) -> Dict[str, Any]:
     path = os.path.join(model_dir, "config.json")
     if not os.path.isfile(path):

@@ -94,10 +94,66 @@ struct AttnArgs {
   // Narrow bf16 family: CTAs of a thread-block cluster that share one work item (1, 2, 4, 8).
   int cluster;
   float scale_log2;  // softmax scale * log2(e)
+  // Changes to a score before the softmax (float32, wide and narrow families; the launcher
+  // refuses them for the tensor-memory family).  With s = (q . k) * scale:
+  //   softcap > 0:  s <- softcap * tanh(s / softcap)
+  //   bias_r1/r2 :  s <- s - r1[h] * ln(1 + r2[h] * (pos - n)), h the query head (null: none)
+  //   chunk > 0  :  a row at position pos sees key n only if n >= (pos / chunk) * chunk
+  //   row_scale  :  s <- s * row_scale[pos], a table over positions (null: none), before the others
+  //   sink_zero  :  one more term of score 0 and no value in every row's softmax denominator.
+  //                 It is put into the running sum of the work item (and warp, and cluster rank)
+  //                 that starts at key 0, which every row of a layer without window or chunk has
+  //                 exactly once however its key range is cut.
+  float scale;  // the softmax scale itself
+  float softcap;
+  const float* bias_r1;
+  const float* bias_r2;
+  const float* row_scale;
+  int row_scale_len;
+  int chunk;
+  int sink_zero;
 };
 
-__device__ __forceinline__ bool key_visible(int n, int pos, int kv_begin, int kv_end, int window, int keep_first) {
-  return n >= kv_begin && n < kv_end && n <= pos && (window <= 0 || n > pos - window || n < keep_first);
+__device__ __forceinline__ bool key_visible(int n, int pos, int kv_begin, int kv_end, int window, int keep_first,
+                                            int chunk_lo = 0) {
+  return n >= kv_begin && n < kv_end && n <= pos && n >= chunk_lo &&
+         (window <= 0 || n > pos - window || n < keep_first);
+}
+
+// First key of the chunk that position pos lies in (0 without chunks).
+__device__ __forceinline__ int chunk_start(int pos, int chunk) {
+  return chunk > 0 && pos > 0 ? (pos / chunk) * chunk : 0;
+}
+
+__device__ __forceinline__ bool has_score_mods(const AttnArgs& a) {
+  return a.softcap > 0.f || a.bias_r1 != nullptr || a.row_scale != nullptr;
+}
+
+// The factor on the scores of a row at position pos (the softmax scale included).
+__device__ __forceinline__ float row_scale_of(const AttnArgs& a, int pos) {
+  if (a.row_scale == nullptr || pos < 0) return a.scale;
+  return a.scale * a.row_scale[pos < a.row_scale_len ? pos : a.row_scale_len - 1];
+}
+
+// The changed score in natural units, from s = (q . k) * scale.  FAST: special-function-unit
+// approximations (absolute error of tanh about 1e-7, relative error of the logarithm 2^-22);
+// else the accurate library functions (the float32 family).
+template <bool FAST>
+__device__ __forceinline__ float mod_score(float s, float softcap, float r1, float r2, int dist) {
+  if (softcap > 0.f) {
+    if (FAST) {
+      float e;
+      asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(e) : "f"(s * (2.885390081777927f / softcap)));  // exp(2 s / cap)
+      s = softcap * (1.0f - __fdividef(2.0f, e + 1.0f));
+    } else {
+      s = softcap * tanhf(s / softcap);
+    }
+  }
+  if (r1 != 0.f) {
+    const float x = r2 * (float)(dist > 0 ? dist : 0);
+    s -= r1 * (FAST ? __log2f(1.0f + x) * 0.6931471805599453f : log1pf(x));
+  }
+  return s;
 }
 
 // =============================================================================================
@@ -143,15 +199,26 @@ __global__ void __launch_bounds__(128) attn_f32_kernel(AttnArgs a) {
   }
 
   float m[F_RPW], l[F_RPW], acc[F_RPW][F_DV];
-  int pos[F_RPW];
+  int pos[F_RPW], chunk_lo[F_RPW];
+  float r1[F_RPW], r2[F_RPW], rs[F_RPW];
+  const bool mods = has_score_mods(a);
+  const bool sink_here = a.sink_zero != 0 && kv_begin == 0;
 #pragma unroll
   for (int i = 0; i < F_RPW; ++i) {
-    m[i] = -CUDART_INF_F;
-    l[i] = 0.f;
+    m[i] = sink_here ? 0.f : -CUDART_INF_F;
+    l[i] = sink_here ? 1.f : 0.f;
 #pragma unroll
     for (int j = 0; j < F_DV; ++j) acc[i][j] = 0.f;
     const int r = warp * F_RPW + i;
     pos[i] = r < row_count ? ctx + (row_begin + r) / a.group : -1;
+    chunk_lo[i] = chunk_start(pos[i], a.chunk);
+    rs[i] = row_scale_of(a, pos[i]);
+    r1[i] = r2[i] = 0.f;
+    if (a.bias_r1 != nullptr && r < row_count) {
+      const int head = kvh * a.group + (row_begin + r) % a.group;
+      r1[i] = a.bias_r1[head];
+      r2[i] = a.bias_r2[head];
+    }
   }
 
   for (int n0 = (kv_begin / F_BN) * F_BN; n0 < kv_end; n0 += F_BN) {
@@ -183,9 +250,12 @@ __global__ void __launch_bounds__(128) attn_f32_kernel(AttnArgs a) {
       if (pos[i] < 0) continue;
       float s = 0.f;
       for (int d = 0; d < D; ++d) s = fmaf(q_s[r][d], k_s[lane][d], s);
-      s *= a.scale_log2;
       const int n = n0 + lane;
-      if (!key_visible(n, pos[i], kv_begin, kv_end, a.window, a.keep_first)) s = -CUDART_INF_F;
+      if (mods)
+        s = mod_score<false>(s * rs[i], a.softcap, r1[i], r2[i], pos[i] - n) * 1.4426950408889634f;
+      else
+        s *= a.scale_log2;
+      if (!key_visible(n, pos[i], kv_begin, kv_end, a.window, a.keep_first, chunk_lo[i])) s = -CUDART_INF_F;
       const float m_new = fmaxf(m[i], warp_max(s));
       const float m_safe = m_new == -CUDART_INF_F ? 0.f : m_new;
       const float p = exp2f(s - m_safe);
@@ -475,7 +545,9 @@ template <int NT>
 __device__ __forceinline__ void softmax_step(float (&s)[NT][4], float (&o)[D / 8][4],
                                              float (&m)[2], float (&l)[2], const int (&pos)[2],
                                              int nbase, int kv_begin, int kv_end, int window, int keep_first,
-                                             float scale_log2, int lane) {
+                                             float scale_log2, int lane, const AttnArgs& a, bool mods,
+                                             const int (&chunk_lo)[2], const float (&r1)[2], const float (&r2)[2],
+                                             const float (&rs)[2]) {
   float mx[2] = {-CUDART_INF_F, -CUDART_INF_F};
 #pragma unroll
   for (int j = 0; j < NT; ++j)
@@ -483,8 +555,12 @@ __device__ __forceinline__ void softmax_step(float (&s)[NT][4], float (&o)[D / 8
     for (int e = 0; e < 4; ++e) {
       const int n = nbase + j * 8 + 2 * (lane & 3) + (e & 1);
       const int h = e >> 1;
-      float v = s[j][e] * scale_log2;
-      if (pos[h] < 0 || !key_visible(n, pos[h], kv_begin, kv_end, window, keep_first)) v = -CUDART_INF_F;
+      float v;
+      if (mods)
+        v = mod_score<true>(s[j][e] * rs[h], a.softcap, r1[h], r2[h], pos[h] - n) * 1.4426950408889634f;
+      else
+        v = s[j][e] * scale_log2;
+      if (pos[h] < 0 || !key_visible(n, pos[h], kv_begin, kv_end, window, keep_first, chunk_lo[h])) v = -CUDART_INF_F;
       s[j][e] = v;
       mx[h] = fmaxf(mx[h], v);
     }
@@ -970,13 +1046,25 @@ __global__ void __launch_bounds__(128) attn_wide_kernel(const __grid_constant__ 
   for (int jd = 0; jd < D / 8; ++jd)
 #pragma unroll
     for (int e = 0; e < 4; ++e) o[jd][e] = 0.f;
-  float m[2] = {-CUDART_INF_F, -CUDART_INF_F}, l[2] = {0.f, 0.f};
+  // A sink of score 0 starts the running sum of the item that begins at key 0.
+  const bool sink_here = a.sink_zero != 0 && kv_begin == 0;
+  float m[2] = {sink_here ? 0.f : -CUDART_INF_F, sink_here ? 0.f : -CUDART_INF_F};
+  float l[2] = {sink_here ? 1.f : 0.f, sink_here ? 1.f : 0.f};
   const int row0 = warp * 16;  // first row this warp works on
-  int pos[2];
+  int pos[2], chunk_lo[2];
+  float r1[2] = {0.f, 0.f}, r2[2] = {0.f, 0.f}, rs[2];
+  const bool mods = has_score_mods(a);
 #pragma unroll
   for (int h = 0; h < 2; ++h) {
     const int r = row0 + (lane >> 2) + 8 * h;
     pos[h] = r < row_count ? ctx + (row_begin + r) / a.group : -1;
+    chunk_lo[h] = chunk_start(pos[h], a.chunk);
+    rs[h] = row_scale_of(a, pos[h]);
+    if (a.bias_r1 != nullptr && r < row_count) {
+      const int head = kvh * a.group + (row_begin + r) % a.group;
+      r1[h] = a.bias_r1[head];
+      r2[h] = a.bias_r2[head];
+    }
   }
 
   int stage = 0, fill = STAGES - 1;
@@ -993,7 +1081,8 @@ __global__ void __launch_bounds__(128) attn_wide_kernel(const __grid_constant__ 
       const __nv_bfloat16* v_s = k_s + TILE;
       float s[NT][4];
       warp_qk<NT>(s, q_s + row0 * B_LD, k_s, 0, lane);
-      softmax_step<NT>(s, o, m, l, pos, n0, kv_begin, kv_end, a.window, a.keep_first, a.scale_log2, lane);
+      softmax_step<NT>(s, o, m, l, pos, n0, kv_begin, kv_end, a.window, a.keep_first, a.scale_log2, lane, a, mods,
+                       chunk_lo, r1, r2, rs);
       warp_pv<NT>(o, s, v_s, 0, lane);
     }
     __syncthreads();  // everyone is done with this stage before it is refilled
@@ -1049,10 +1138,15 @@ struct NarrowWarp {
   float o[D / 16][NR][4];
   float m[NR][2], l[NR][2];
   int pos[NR][2];
+  // Score changes (see AttnArgs): the first key of a row's chunk and its head's two bias numbers.
+  int chunk_lo[NR][2];
+  float r1[NR][2], r2[NR][2], rs[NR][2];
   uint32_t qb[D / 16][2 * NR];
 
+  // sink: this warp starts every row's sum with a term of score 0 (one lane of the eight that
+  // share a row holds it).
   __device__ __forceinline__ void init(const __nv_bfloat16* q_s, int row_begin, int row_count,
-                                       int ctx, int group, int lane) {
+                                       int ctx, int group, int lane, const AttnArgs& a, int kvh, bool sink) {
 #pragma unroll
     for (int mt = 0; mt < D / 16; ++mt)
 #pragma unroll
@@ -1063,10 +1157,18 @@ struct NarrowWarp {
     for (int j = 0; j < NR; ++j)
 #pragma unroll
       for (int i = 0; i < 2; ++i) {
-        m[j][i] = -CUDART_INF_F;
-        l[j][i] = 0.f;
+        m[j][i] = sink ? 0.f : -CUDART_INF_F;
+        l[j][i] = sink && (lane >> 2) == 0 ? 1.f : 0.f;
         const int r = 8 * j + 2 * (lane & 3) + i;
         pos[j][i] = r < row_count ? ctx + (row_begin + r) / group : -1;
+        chunk_lo[j][i] = chunk_start(pos[j][i], a.chunk);
+        rs[j][i] = row_scale_of(a, pos[j][i]);
+        r1[j][i] = r2[j][i] = 0.f;
+        if (a.bias_r1 != nullptr && r < row_count) {
+          const int head = kvh * group + (row_begin + r) % group;
+          r1[j][i] = a.bias_r1[head];
+          r2[j][i] = a.bias_r2[head];
+        }
       }
     // Q as the B operand, kept for the whole item: matrices (rows 0-7, dims lo), (rows 0-7,
     // dims hi), (rows 8-15, dims lo), (rows 8-15, dims hi) of every 16-dim step.
@@ -1082,7 +1184,7 @@ struct NarrowWarp {
   // Keys [n0 + key0, n0 + key0 + 16) of the tile in k_s / v_s.
   __device__ __forceinline__ void tile(const __nv_bfloat16* k_s, const __nv_bfloat16* v_s, int key0,
                                        int nbase, int kv_begin, int kv_end, int window, int keep_first,
-                                       float scale_log2, int lane) {
+                                       float scale_log2, int lane, const AttnArgs& a, bool mods) {
     float s[NR][4];
 #pragma unroll
     for (int j = 0; j < NR; ++j)
@@ -1104,6 +1206,17 @@ struct NarrowWarp {
     // holds as well as 1), so that most tiles rescale nothing.  l is this thread's share of
     // the row's sum; the lanes' shares are added up once, in write_rows().
     const int g = lane >> 2;
+    if (mods) {
+      // The changed scores, in natural units; the exponent's multiply-add then only converts
+      // to base 2.
+#pragma unroll
+      for (int j = 0; j < NR; ++j)
+#pragma unroll
+        for (int e = 0; e < 4; ++e)
+          s[j][e] = mod_score<true>(s[j][e] * rs[j][e & 1], a.softcap, r1[j][e & 1], r2[j][e & 1],
+                                    pos[j][e & 1] - (nbase + g + 8 * (e >> 1)));
+      scale_log2 = 1.4426950408889634f;
+    }
     bool sees_all = true;
 #pragma unroll
     for (int j = 0; j < NR; ++j)
@@ -1112,7 +1225,7 @@ struct NarrowWarp {
         const int p = pos[j][i];
         if (p >= 0)
           sees_all = sees_all && nbase >= kv_begin && nbase + 16 <= kv_end && nbase + 15 <= p &&
-                     (window <= 0 || nbase > p - window);
+                     nbase >= chunk_lo[j][i] && (window <= 0 || nbase > p - window);
       }
     if (!__all_sync(0xffffffffu, sees_all)) {
 #pragma unroll
@@ -1120,7 +1233,8 @@ struct NarrowWarp {
 #pragma unroll
         for (int e = 0; e < 4; ++e) {
           const int p = pos[j][e & 1];
-          if (p >= 0 && !key_visible(nbase + g + 8 * (e >> 1), p, kv_begin, kv_end, window, keep_first))
+          if (p >= 0 && !key_visible(nbase + g + 8 * (e >> 1), p, kv_begin, kv_end, window, keep_first,
+                                     chunk_lo[j][e & 1]))
             s[j][e] = -CUDART_INF_F;
         }
     }
@@ -1321,6 +1435,9 @@ __global__ void __launch_bounds__(NARROW_THREADS) attn_narrow_kernel(const __gri
 
   // Keys past the last row's position are hidden from every row of the item.
   const int last_pos = ctx + (row_begin + row_count - 1) / a.group;
+  // A sink of score 0 starts the running sum of one warp of the CTA whose keys begin at key 0.
+  const bool sink_cta = a.sink_zero != 0 && kv_begin == 0 && (cluster <= 1 || cluster_rank() == 0);
+  const bool mods = has_score_mods(a);
   if (cluster > 1) {
     // The item's key tiles, dealt out in runs: rank r gets tiles [r * per, (r + 1) * per).
     const int visible_end = min(kv_end, last_pos + 1);
@@ -1403,7 +1520,7 @@ __global__ void __launch_bounds__(NARROW_THREADS) attn_narrow_kernel(const __gri
   float* ml = mm + WARPS * 16;                      // [WARPS][16]
   auto consume = [&](auto& state) {
     if (warp < WARPS) {
-      state.init(q_s, row_begin, row_count, ctx, a.group, lane);
+      state.init(q_s, row_begin, row_count, ctx, a.group, lane, a, kvh, sink_cta && warp == 0);
       const int group = warp >> 2;
       const int key0 = (warp & 3) * 16;  // the keys of a tile this warp works on
       bool alive = true;
@@ -1414,7 +1531,8 @@ __global__ void __launch_bounds__(NARROW_THREADS) attn_narrow_kernel(const __gri
         if (t == group) VX_TRACE_MARK(2);
         if (alive) {
           const __nv_bfloat16* k_s = kv_s + st * 2 * TILE;
-          state.tile(k_s, k_s + TILE, key0, n0 + key0, kv_begin, kv_end, a.window, a.keep_first, a.scale_log2, lane);
+          state.tile(k_s, k_s + TILE, key0, n0 + key0, kv_begin, kv_end, a.window, a.keep_first, a.scale_log2, lane,
+                     a, mods);
         }
         __syncwarp();
         if (lane == 0) mbar_arrive(smem_u32(&kv_empty[st]));  // this warp has read the stage
@@ -2236,7 +2354,9 @@ static AttnArgs make_args(const void* q, void* out, const void* k_cache, const v
                           float* partial_lse, const int* merge_items, int* split_counters,
                           int q_stride, int out_stride, int table_stride,
                           int num_kv_heads, int group, int page_size, int window,
-                          float softmax_scale, int keep_first = 0) {
+                          float softmax_scale, int keep_first = 0, float softcap = 0.f,
+                          const float* bias_r1 = nullptr, const float* bias_r2 = nullptr, int chunk = 0,
+                          int sink_zero = 0, const float* row_scale = nullptr, int row_scale_len = 0) {
   AttnArgs a;
   memset(&a, 0, sizeof(a));
   a.q = q;
@@ -2265,6 +2385,14 @@ static AttnArgs make_args(const void* q, void* out, const void* k_cache, const v
   a.sinks = nullptr;
   a.cluster = 1;
   a.scale_log2 = softmax_scale * 1.4426950408889634f;
+  a.scale = softmax_scale;
+  a.softcap = softcap > 0.f ? softcap : 0.f;
+  a.bias_r1 = bias_r2 != nullptr ? bias_r1 : nullptr;
+  a.bias_r2 = bias_r1 != nullptr ? bias_r2 : nullptr;
+  a.chunk = chunk > 0 ? chunk : 0;
+  a.sink_zero = sink_zero;
+  a.row_scale = row_scale_len > 0 ? row_scale : nullptr;
+  a.row_scale_len = row_scale_len;
   return a;
 }
 
@@ -2282,15 +2410,22 @@ VX_API int vx_attn_has_tc() {
 #endif
 }
 
-// kind: 0 = float32, 1 = bf16 wide (64 rows), 2 = bf16 narrow (16 rows).
-VX_API int vx_attention(int kind, const void* q, void* out, const void* k_cache,
-                        const void* v_cache, const int* block_tables, const int* q_start,
-                        const int* q_len, const int* kv_len, const int* items, int num_items,
-                        int* status, float* partial_o, float* partial_lse, const int* merge_items,
-                        int* split_counters, int q_stride, int out_stride, int table_stride,
-                        int num_kv_heads, int group, int page_size, long long num_pages,
-                        int window, float softmax_scale, int cluster, int keep_first, cudaStream_t stream) {
+// kind: 0 = float32, 1 = bf16 wide (64 rows), 2 = bf16 narrow (16 rows), 3 = tensor memory.
+// softcap, bias_r1 / bias_r2 (one float per query head), chunk and sink_zero change the scores
+// as AttnArgs says; the tensor-memory family takes none of them.
+VX_API int vx_attention_scored(int kind, const void* q, void* out, const void* k_cache,
+                               const void* v_cache, const int* block_tables, const int* q_start,
+                               const int* q_len, const int* kv_len, const int* items, int num_items,
+                               int* status, float* partial_o, float* partial_lse, const int* merge_items,
+                               int* split_counters, int q_stride, int out_stride, int table_stride,
+                               int num_kv_heads, int group, int page_size, long long num_pages,
+                               int window, float softmax_scale, int cluster, int keep_first, float softcap,
+                               const float* bias_r1, const float* bias_r2, int chunk, int sink_zero,
+                               const float* row_scale, int row_scale_len, cudaStream_t stream) {
   if (num_items <= 0) return 0;
+  const bool changed = softcap > 0.f || bias_r1 != nullptr || chunk > 0 || sink_zero != 0 || row_scale != nullptr;
+  if (changed && kind == 3) return (int)cudaErrorInvalidValue;
+  if (sink_zero != 0 && (window > 0 || chunk > 0)) return (int)cudaErrorInvalidValue;
   // Only the narrow bf16 family shares an item among the CTAs of a cluster; for the
   // tensor-memory family 2 means "two CTAs on an SM" (see its launch below).
   if (cluster != 1 && !(kind == 3 && cluster == 2) &&
@@ -2301,7 +2436,8 @@ VX_API int vx_attention(int kind, const void* q, void* out, const void* k_cache,
   AttnArgs a = make_args(q, out, k_cache, v_cache, block_tables, q_start, q_len, kv_len,
                                items, status, partial_o, partial_lse, merge_items, split_counters,
                                q_stride, out_stride, table_stride,
-                               num_kv_heads, group, page_size, window, softmax_scale, keep_first);
+                               num_kv_heads, group, page_size, window, softmax_scale, keep_first,
+                               softcap, bias_r1, bias_r2, chunk, sink_zero, row_scale, row_scale_len);
   if (kind != 0 && TMA_KV) {
     // Page sizes are powers of two: a 64-key tile is whole pages, or lies inside one page.
     if (page_size <= 0 || (page_size & (page_size - 1)) != 0) return -1;
@@ -2415,6 +2551,20 @@ VX_API int vx_attention(int kind, const void* q, void* out, const void* k_cache,
     return (int)cudaErrorInvalidValue;
   }
   return (int)cudaGetLastError();
+}
+
+// The same without changes to the scores.
+VX_API int vx_attention(int kind, const void* q, void* out, const void* k_cache,
+                        const void* v_cache, const int* block_tables, const int* q_start,
+                        const int* q_len, const int* kv_len, const int* items, int num_items,
+                        int* status, float* partial_o, float* partial_lse, const int* merge_items,
+                        int* split_counters, int q_stride, int out_stride, int table_stride,
+                        int num_kv_heads, int group, int page_size, long long num_pages,
+                        int window, float softmax_scale, int cluster, int keep_first, cudaStream_t stream) {
+  return vx_attention_scored(kind, q, out, k_cache, v_cache, block_tables, q_start, q_len, kv_len, items,
+                             num_items, status, partial_o, partial_lse, merge_items, split_counters, q_stride,
+                             out_stride, table_stride, num_kv_heads, group, page_size, num_pages, window,
+                             softmax_scale, cluster, keep_first, 0.f, nullptr, nullptr, 0, 0, nullptr, 0, stream);
 }
 
 // What the planner needs to know about the narrow family: how many of its CTAs an SM holds

@@ -1,9 +1,10 @@
 """Compiles the CUDA sources of this directory for sm_100a and loads them with ctypes.
 
-There are three libraries: ``core`` (row-wise kernels, sampling, GEMMs; one build),
-``attention`` (one build per head size, ``-DVX_HEAD_DIM=<D>``) and ``mixers`` (recurrent mixers
-and expert feed-forwards; one build), so a process compiles what its model needs and nothing
-else.  A build is keyed by a hash of its sources, flags and compiler
+There are four libraries: ``core`` (row-wise kernels, sampling, GEMMs; one build),
+``attention`` (one build per head size, ``-DVX_HEAD_DIM=<D>``), ``mixers`` (recurrent mixers
+and expert feed-forwards; one build) and ``heads`` (token shift, differential attention's two
+ends, the clamped gated activation; one build), so a process compiles what its model needs and
+nothing else.  A build is keyed by a hash of its sources, flags and compiler
 version; it is made once and reused.  Builds go to ``velox_b200/_build`` inside the package when
 that is writable, else to ``$VELOX_B200_BUILD_DIR``, else to a per-user folder under the
 system's temporary directory.  nvcc cross-compiles without a GPU, so the build also runs on a
@@ -39,6 +40,8 @@ CORE_SOURCES = ("core.cu", "sampling.cu", "gemm_bf16.cu", "residual.cu", "latent
 # Mixers with a state of fixed size per request and feed-forwards with experts: built only for
 # models that have such parts.
 MIXER_SOURCES = ("sequence.cu", "routed.cu")
+# Row kernels around attention heads and gated feed-forwards: built for models with such parts.
+HEADS_SOURCES = ("heads.cu",)
 ATTENTION_SOURCES = ("attention.cu",)
 HEADERS = ("common.cuh", "attention_static.h")
 
@@ -191,6 +194,10 @@ def load_mixers() -> ctypes.CDLL:
     return _load("mixers", MIXER_SOURCES, ())
 
 
+def load_heads() -> ctypes.CDLL:
+    return _load("heads", HEADS_SOURCES, ())
+
+
 def load_attention(head_dim: int) -> ctypes.CDLL:
     if head_dim % 16 != 0 or not 16 <= head_dim <= 256:
         raise ValueError(
@@ -215,7 +222,8 @@ def _load(name: str, sources: Sequence[str], defines: Sequence[str]) -> ctypes.C
 
 def build_all(head_dims: Iterable[int] = (128,)) -> List[str]:
     """Compile every library (for the given head sizes) without loading anything."""
-    paths = [build_library("core", CORE_SOURCES, ()), build_library("mixers", MIXER_SOURCES, ())]
+    paths = [build_library("core", CORE_SOURCES, ()), build_library("mixers", MIXER_SOURCES, ()),
+             build_library("heads", HEADS_SOURCES, ())]
     for head_dim in head_dims:
         paths.append(
             build_library(f"attention_d{head_dim}", ATTENTION_SOURCES, (f"-DVX_HEAD_DIM={head_dim}",))

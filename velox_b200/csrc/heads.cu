@@ -1,0 +1,314 @@
+// Row kernels around attention heads and gated feed-forwards (the `heads` library; float32 and
+// bfloat16 instantiations of each):
+//
+//   norm_shift_kernel        one RMS statistic per row, two weighted outputs; the first output is
+//                            mixed with the previous token's (token shift), whose last value per
+//                            request lives in a slot-indexed state row
+//   add_rows_kernel          stream += a (+ b), float32 sums
+//   diff_prepare_kernel      differential attention: per (head, map) RMS norm of q and k, rotation
+//                            of the first dims of every map, q into a buffer whose "heads" are
+//                            (head, map) pairs with the map's dims at the map's offset, k of both
+//                            maps side by side into one cached row, v into its page
+//   diff_combine_kernel      o = a1 - lambda a2, unit RMS over the head, times (1 - lambda_init),
+//                            times sigmoid(gate)
+//   clamped_glu_kernel       g = min(g, limit), u = clamp(u, +-limit), g sigmoid(alpha g) (u + shift)
+//
+// Everything between the loads and the stores is float32.  Every sum has an order that depends
+// on the sizes only.
+#include "common.cuh"
+
+#include <math_constants.h>
+
+namespace vx {
+
+__device__ __forceinline__ float hd_sigmoid(float v) { return 1.0f / (1.0f + expf(-v)); }
+
+// ---------------------------------------------------------------------------------------------
+// Token shift.  With h_t = x_t / rms(x_t) * w1 the first output of row t is
+//     h_t + (h_(t-1) - h_t) * shift
+// where h_(t-1) is the same norm of the request's previous token: recomputed from row t - 1 when
+// that row is in this step, read from the request's state row when t is the first row of its
+// portion (zero for the first token of a request: a state row is zero when a slot is taken).
+// The block of a portion's first row also writes the portion's last h into the state row, after
+// it has read it, so no other block touches the row.  The second output is x_t / rms(x_t) * w2.
+// One block per row.
+template <typename T>
+__global__ void norm_shift_kernel(const float* __restrict__ resid, long long resid_stride, int width, float eps,
+                                  const float* __restrict__ w1, const float* __restrict__ w2,
+                                  const float* __restrict__ shift, float* __restrict__ state,
+                                  long long state_stride, T* __restrict__ out1, T* __restrict__ out2,
+                                  const int* __restrict__ q_start, const int* __restrict__ q_len,
+                                  const int* __restrict__ seq_slots, int num_seqs) {
+  __shared__ float scratch[32];
+  allow_dependents();
+  const int t = blockIdx.x;
+  // Which request's row this is (rows of no request: padding of a rounded step).
+  int seq = -1, first = 0, last = 0;
+  for (int s = 0; s < num_seqs; ++s) {
+    const int b = q_start[s], n = q_len[s];
+    if (n > 0 && t >= b && t < b + n) {
+      seq = s;
+      first = b;
+      last = b + n - 1;
+    }
+  }
+  grid_dependency_wait();
+  const float* x = resid + (size_t)t * resid_stride;
+  float ss = 0.f;
+  for (int i = threadIdx.x; i < width; i += blockDim.x) ss += x[i] * x[i];
+  const float r = rsqrtf(block_sum(ss, scratch) / (float)width + eps);
+  const bool shifted = shift != nullptr;
+  const float* prev_x = nullptr;
+  const float* prev_h = nullptr;
+  float prev_r = 0.f;
+  if (shifted && seq >= 0) {
+    if (t > first) {
+      prev_x = x - resid_stride;
+      float ps = 0.f;
+      for (int i = threadIdx.x; i < width; i += blockDim.x) ps += prev_x[i] * prev_x[i];
+      prev_r = rsqrtf(block_sum(ps, scratch) / (float)width + eps);
+    } else {
+      prev_h = state + (size_t)seq_slots[seq] * state_stride;
+    }
+  }
+  for (int i = threadIdx.x; i < width; i += blockDim.x) {
+    const float n = x[i] * r;
+    float h = n * w1[i];
+    if (shifted) {
+      const float before = prev_x != nullptr ? prev_x[i] * prev_r * w1[i] : (prev_h != nullptr ? prev_h[i] : 0.f);
+      h = h + (before - h) * shift[i];
+    }
+    out1[(size_t)t * width + i] = from_float<T>(h);
+    if (w2 != nullptr) out2[(size_t)t * width + i] = from_float<T>(n * w2[i]);
+  }
+  if (shifted && seq >= 0 && t == first) {
+    // The portion's last row, normed once more, is what the next step's first row looks back at.
+    __syncthreads();
+    const float* xl = resid + (size_t)last * resid_stride;
+    float ls = 0.f;
+    for (int i = threadIdx.x; i < width; i += blockDim.x) ls += xl[i] * xl[i];
+    const float lr = rsqrtf(block_sum(ls, scratch) / (float)width + eps);
+    float* dst = state + (size_t)seq_slots[seq] * state_stride;
+    for (int i = threadIdx.x; i < width; i += blockDim.x) dst[i] = xl[i] * lr * w1[i];
+  }
+}
+
+template <typename T>
+__global__ void add_rows_kernel(float* __restrict__ resid, const T* __restrict__ a, const T* __restrict__ b,
+                                long long count) {
+  allow_dependents();
+  grid_dependency_wait();
+  for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < count;
+       i += (long long)gridDim.x * blockDim.x) {
+    float v = resid[i] + to_float(a[i]);
+    if (b != nullptr) v += to_float(b[i]);
+    resid[i] = v;
+  }
+}
+
+// ---------------------------------------------------------------------------------------------
+// Differential attention, before the attention kernels.  The projection's row of token t holds
+// q [H][2][dim] | k [G][2][dim] | v [G][vdim] | (further columns).  A warp takes one unit:
+//   q unit (h, m): RMS norm over dim times q_norm, rotation, into qbuf[t][2 h + m][m * dim + i];
+//                  the other entries of the D-wide head stay zero, so its product with the cached
+//                  row [k map 0 | k map 1 | 0] is the score of map m alone
+//   k unit (g, m): the same with k_norm, into k_cache[slot][g][m * dim + i]
+//   v unit g     : copied into v_cache[slot][g][i]
+// Rotation: dims i and i + rot / 2 (i < rot / 2) of a map are a pair that turns by the tabulated
+// angle of (position, i).
+template <typename T>
+__global__ void diff_prepare_kernel(const T* __restrict__ proj, long long stride, T* __restrict__ qbuf,
+                                    long long q_stride, const int* __restrict__ positions,
+                                    const float* __restrict__ cos_t, const float* __restrict__ sin_t,
+                                    const float* __restrict__ q_norm, const float* __restrict__ k_norm, float eps,
+                                    const int* __restrict__ slots, T* __restrict__ k_cache, T* __restrict__ v_cache,
+                                    int H, int G, int dim, int vdim, int D, int rot, int max_pos,
+                                    long long num_slots, int write_cache, int* status) {
+  allow_dependents();
+  grid_dependency_wait();
+  const int t = blockIdx.x;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int unit = blockIdx.y * (blockDim.x >> 5) + warp;
+  const int q_units = 2 * H, k_units = 2 * G;
+  if (unit >= q_units + k_units + G) return;
+  const T* row = proj + (size_t)t * stride;
+  int slot = -1;
+  if (unit >= q_units) {
+    if (!write_cache) return;
+    slot = slots[t];
+    if (slot < 0) return;
+    if ((long long)slot >= num_slots) {
+      if (lane == 0) atomicOr(status, VX_STATUS_BAD_SLOT);
+      return;
+    }
+  }
+  if (unit >= q_units + k_units) {
+    const int g = unit - q_units - k_units;
+    const T* src = row + (size_t)(q_units + k_units) * dim + (size_t)g * vdim;
+    T* dst = v_cache + ((size_t)slot * G + g) * D;
+    for (int i = lane; i < vdim; i += 32) dst[i] = src[i];
+    return;
+  }
+  const bool is_q = unit < q_units;
+  const int u = is_q ? unit : unit - q_units;
+  const int map = u & 1;
+  const T* src = row + (size_t)unit * dim;  // q units first, k units right behind them
+  const float* w = is_q ? q_norm : k_norm;
+  int pos = positions[t];
+  if (rot > 0 && (pos < 0 || pos >= max_pos)) {
+    if (lane == 0 && unit == 0) atomicOr(status, VX_STATUS_BAD_POSITION);
+    pos = 0;
+  }
+  float ss = 0.f;
+  for (int i = lane; i < dim; i += 32) {
+    const float v = to_float(src[i]);
+    ss += v * v;
+  }
+  const float r = w != nullptr ? rsqrtf(warp_sum(ss) / (float)dim + eps) : 1.0f;
+  T* dst = is_q ? qbuf + (size_t)t * q_stride + (size_t)unit * D + (size_t)map * dim
+                : k_cache + ((size_t)slot * G + (u >> 1)) * D + (size_t)map * dim;
+  const int half = rot >> 1;
+  const float* c = cos_t + (size_t)pos * half;
+  const float* s = sin_t + (size_t)pos * half;
+  for (int i = lane; i < dim; i += 32) {
+    float v = to_float(src[i]) * r * (w != nullptr ? w[i] : 1.0f);
+    if (i < rot) {
+      const int j = i < half ? i : i - half;
+      const int other = i < half ? i + half : i - half;
+      const float o = to_float(src[other]) * r * (w != nullptr ? w[other] : 1.0f);
+      // (u, v) -> (u cos - v sin, v cos + u sin) for the pair (j, j + half)
+      v = i < half ? v * c[j] - o * s[j] : v * c[j] + o * s[j];
+    }
+    dst[i] = from_float<T>(v);
+  }
+}
+
+// After the attention kernels: attn[t][2 h + m][0 .. vdim) is map m of head h.  A warp per
+// (token, head).
+template <typename T>
+__global__ void diff_combine_kernel(const T* __restrict__ attn, long long attn_stride, const T* __restrict__ gate,
+                                    long long gate_stride, T* __restrict__ out, long long out_stride, int H,
+                                    int vdim, int D, float lambda, float out_scale, float eps) {
+  allow_dependents();
+  grid_dependency_wait();
+  const int t = blockIdx.x;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int h = blockIdx.y * (blockDim.x >> 5) + warp;
+  if (h >= H) return;
+  const T* a1 = attn + (size_t)t * attn_stride + (size_t)(2 * h) * D;
+  const T* a2 = a1 + D;
+  float ss = 0.f;
+  for (int i = lane; i < vdim; i += 32) {
+    const float o = to_float(a1[i]) - lambda * to_float(a2[i]);
+    ss += o * o;
+  }
+  const float r = rsqrtf(warp_sum(ss) / (float)vdim + eps) * out_scale;
+  const T* g = gate != nullptr ? gate + (size_t)t * gate_stride + (size_t)h * vdim : nullptr;
+  T* dst = out + (size_t)t * out_stride + (size_t)h * vdim;
+  for (int i = lane; i < vdim; i += 32) {
+    float o = (to_float(a1[i]) - lambda * to_float(a2[i])) * r;
+    if (g != nullptr) o *= hd_sigmoid(to_float(g[i]));
+    dst[i] = from_float<T>(o);
+  }
+}
+
+// gate_up [tokens][2 F] (gate columns first) -> out [tokens][F].
+template <typename T>
+__global__ void clamped_glu_kernel(const T* __restrict__ gate_up, long long in_stride, T* __restrict__ out,
+                                   long long out_stride, int F, float limit, float alpha, float up_shift,
+                                   long long count) {
+  allow_dependents();
+  grid_dependency_wait();
+  for (long long idx = (long long)blockIdx.x * blockDim.x + threadIdx.x; idx < count;
+       idx += (long long)gridDim.x * blockDim.x) {
+    const long long t = idx / F;
+    const int f = (int)(idx - t * F);
+    float g = to_float(gate_up[t * in_stride + f]);
+    float u = to_float(gate_up[t * in_stride + F + f]);
+    if (limit > 0.f) {
+      g = fminf(g, limit);
+      u = fminf(fmaxf(u, -limit), limit);
+    }
+    out[t * out_stride + f] = from_float<T>(g * hd_sigmoid(alpha * g) * (u + up_shift));
+  }
+}
+
+}  // namespace vx
+
+using namespace vx;
+
+#define VX_BY_DTYPE(dtype, call)                  \
+  if ((dtype) == VX_DTYPE_F32) {                  \
+    using T = float;                              \
+    call;                                         \
+  } else if ((dtype) == VX_DTYPE_BF16) {          \
+    using T = __nv_bfloat16;                      \
+    call;                                         \
+  } else {                                        \
+    return (int)cudaErrorInvalidValue;            \
+  }
+
+static int row_threads(int width) {
+  const int t = (width + 31) / 32 * 32;
+  return t > 512 ? 512 : (t < 32 ? 32 : t);
+}
+
+VX_API int vx_norm_shift(const float* resid, long long resid_stride, int width, float eps, const float* w1,
+                         const float* w2, const float* shift, float* state, long long state_stride, void* out1,
+                         void* out2, int dtype, const int* q_start, const int* q_len, const int* seq_slots,
+                         int num_seqs, int num_tokens, cudaStream_t stream) {
+  if (num_tokens <= 0) return 0;
+  if (shift != nullptr && state == nullptr) return (int)cudaErrorInvalidValue;
+  VX_BY_DTYPE(dtype, launch_pdl(norm_shift_kernel<T>, dim3(num_tokens), dim3(row_threads(width)), 0, stream, resid,
+                                resid_stride, width, eps, w1, w2, shift, state, state_stride, (T*)out1, (T*)out2,
+                                q_start, q_len, seq_slots, num_seqs));
+  return (int)cudaGetLastError();
+}
+
+VX_API int vx_add_rows(float* resid, const void* a, const void* b, int dtype, long long count, cudaStream_t stream) {
+  if (count <= 0) return 0;
+  long long blocks = (count + 255) / 256;
+  if (blocks > 148 * 16) blocks = 148 * 16;
+  VX_BY_DTYPE(dtype, launch_pdl(add_rows_kernel<T>, dim3((unsigned)blocks), dim3(256), 0, stream, resid,
+                                (const T*)a, (const T*)b, count));
+  return (int)cudaGetLastError();
+}
+
+VX_API int vx_diff_prepare(const void* proj, int dtype, long long stride, void* qbuf, long long q_stride,
+                           const int* positions, const float* cos_t, const float* sin_t, const float* q_norm,
+                           const float* k_norm, float eps, const int* slots, void* k_cache, void* v_cache,
+                           int num_tokens, int H, int G, int dim, int vdim, int D, int rot, int max_pos,
+                           long long num_slots, int write_cache, int* status, cudaStream_t stream) {
+  if (num_tokens <= 0) return 0;
+  if (2 * dim > D || vdim > D || rot > dim || (rot & 1)) return (int)cudaErrorInvalidValue;
+  const int units = 2 * H + 2 * G + G;
+  const dim3 grid(num_tokens, (units + 3) / 4);
+  VX_BY_DTYPE(dtype, launch_pdl(diff_prepare_kernel<T>, grid, dim3(128), 0, stream, (const T*)proj, stride, (T*)qbuf,
+                                q_stride, positions, cos_t, sin_t, q_norm, k_norm, eps, slots, (T*)k_cache,
+                                (T*)v_cache, H, G, dim, vdim, D, rot, max_pos, num_slots, write_cache, status));
+  return (int)cudaGetLastError();
+}
+
+VX_API int vx_diff_combine(const void* attn, int dtype, long long attn_stride, const void* gate,
+                           long long gate_stride, void* out, long long out_stride, int num_tokens, int H, int vdim,
+                           int D, float lambda, float out_scale, float eps, cudaStream_t stream) {
+  if (num_tokens <= 0) return 0;
+  const dim3 grid(num_tokens, (H + 3) / 4);
+  VX_BY_DTYPE(dtype, launch_pdl(diff_combine_kernel<T>, grid, dim3(128), 0, stream, (const T*)attn, attn_stride,
+                                (const T*)gate, gate_stride, (T*)out, out_stride, H, vdim, D, lambda, out_scale,
+                                eps));
+  return (int)cudaGetLastError();
+}
+
+VX_API int vx_clamped_glu(const void* gate_up, int dtype, long long in_stride, void* out, long long out_stride,
+                          int num_tokens, int F, float limit, float alpha, float up_shift, cudaStream_t stream) {
+  if (num_tokens <= 0 || F <= 0) return 0;
+  const long long count = (long long)num_tokens * F;
+  long long blocks = (count + 255) / 256;
+  if (blocks > 148 * 16) blocks = 148 * 16;
+  VX_BY_DTYPE(dtype, launch_pdl(clamped_glu_kernel<T>, dim3((unsigned)blocks), dim3(256), 0, stream,
+                                (const T*)gate_up, in_stride, (T*)out, out_stride, F, limit, alpha, up_shift, count));
+  return (int)cudaGetLastError();
+}
+
+VX_TRACE_API(vx_heads)

@@ -80,18 +80,28 @@ class CausalLM:
         self.entry_group: List[Optional[int]] = []
         by_window: Dict[tuple, int] = {}
         for entry in spec.schedule:
-            needs = self.blocks[entry.layer].mixer.cache_needs()
+            block = self.blocks[entry.layer]
+            needs = block.mixer.cache_needs()
+            state_needs = getattr(block, "state_needs", None)
+            if state_needs is not None and state_needs() is not None:
+                # The arrangement keeps a row per request too (a token shift's previous token).
+                needs = CacheNeeds(paged=needs.paged, state=needs.state, block_state=state_needs())
             self.entry_needs.append(needs)
             if needs.paged is None:
                 self.entry_group.append(None)
                 continue
             window = needs.paged.window
             keep_first = needs.paged.keep_first if window is not None else 0
-            if (window, keep_first) not in by_window:
-                by_window[(window, keep_first)] = len(self.cache_groups)
-                name = "all_keys" if window is None else f"window_{window}" + (f"_keep_{keep_first}" if keep_first else "")
-                self.cache_groups.append(CacheGroup(name=name, window=window, keep_first=keep_first))
-            self.entry_group.append(by_window[(window, keep_first)])
+            chunk = needs.paged.chunk if window is None else 0
+            key = (window, keep_first, chunk)
+            if key not in by_window:
+                by_window[key] = len(self.cache_groups)
+                if window is None:
+                    name = f"chunk_{chunk}" if chunk else "all_keys"
+                else:
+                    name = f"window_{window}" + (f"_keep_{keep_first}" if keep_first else "")
+                self.cache_groups.append(CacheGroup(name=name, window=window, keep_first=keep_first, chunk=chunk))
+            self.entry_group.append(by_window[key])
         if not self.cache_groups:
             # A model without paged state still gets one (empty) group so tables exist.
             self.cache_groups.append(CacheGroup(name="all_keys", window=None))

@@ -30,7 +30,7 @@ import numpy as np
 import torch
 
 from ..cache.manager import CacheManager, SequenceCache
-from ..cache.storage import LayerCache, allocate_layer_cache
+from ..cache.storage import LayerCache, allocate_block_state, allocate_layer_cache
 from ..ops import attention_plan as ap
 from ..ops import kernels
 from .model import CausalLM
@@ -246,7 +246,8 @@ class ModelRunner:
         # Not a planner option: up to how many keys the layout without splits through memory is
         # used for padded single-token steps (tests move it down to their sizes).
         self.short_reach = int(self.plan_overrides.pop("short_reach", self.SHORT_REACH))
-        if [(g.window, g.keep_first) for g in cache.groups] != [(g.window, g.keep_first) for g in model.cache_groups]:
+        if ([(g.window, g.keep_first, g.chunk) for g in cache.groups]
+                != [(g.window, g.keep_first, g.chunk) for g in model.cache_groups]):
             raise ValueError("the cache manager's groups are not the model's cache groups")
 
         self.workspace = Workspace(self.max_tokens, max_logit_rows or max_num_seqs, self.device)
@@ -262,7 +263,8 @@ class ModelRunner:
             if entry.cache_of is not None:
                 owner = self.layer_caches[entry.cache_of]
                 self.layer_caches.append(
-                    LayerCache(group=owner.group, k=owner.k, v=owner.v, state=owner.state, read_only=True)
+                    LayerCache(group=owner.group, k=owner.k, v=owner.v, state=owner.state, read_only=True,
+                               block_state=allocate_block_state(model.entry_needs[index], max_num_seqs, self.device))
                 )
             else:
                 self.layer_caches.append(
@@ -314,6 +316,8 @@ class ModelRunner:
         for layer_cache in self.layer_caches:
             if layer_cache.state is not None and not layer_cache.read_only:
                 layer_cache.state[seq.slot].zero_()
+            if layer_cache.block_state is not None:
+                layer_cache.block_state[seq.slot].zero_()
 
     def kv_cache_bytes(self) -> int:
         return sum(c.num_bytes() for c in self.layer_caches if not c.read_only)
@@ -656,6 +660,9 @@ class ModelRunner:
             # finished by the merge kernel (a sink in the denominator, kept first keys).
             options["keep_first"] = int(signature[4] or 0)
             options["anchored"] = bool(signature[5])
+        if len(signature) > 6:
+            # Further options of the layout by name (a chunked mask, no tensor-memory family).
+            options.update(dict(signature[6]))
         return ap.PlanOptions(**options)
 
     # Key tiles per work item from which the tensor-memory attention runs two CTAs on an SM when
@@ -826,6 +833,8 @@ class ModelRunner:
             if splits <= 1 and not fresh:
                 # Only the key ranges move from step to step.
                 lo = np.maximum(0, kv_lens - opt.window) if opt.window else 0
+                if opt.chunk:
+                    lo = np.maximum(lo, (kv_lens - 1) // opt.chunk * opt.chunk)
                 items_view[:n, 3] = lo
                 items_view[:n, 4] = kv_lens
                 continue

@@ -81,6 +81,8 @@ class PlanOptions:
     # joins the softmax denominator and where the kept first keys (a key range of their own,
     # before the window's) meet the window's keys: see ``plan_anchored``.
     anchored: bool = False
+    # A chunked mask: a query at position p sees keys from floor(p / chunk) * chunk on (0: all).
+    chunk: int = 0
 
 
 def splits_through_memory(span, cluster: int, opt: PlanOptions):
@@ -140,12 +142,15 @@ def choose_cluster(opt: PlanOptions, pairs: int, wanted: int) -> int:
 
 
 def _key_range(q_len: int, kv_len: int, group: int, window: Optional[int], row_begin: int,
-               row_count: int) -> Tuple[int, int]:
+               row_count: int, chunk: int = 0) -> Tuple[int, int]:
     ctx = kv_len - q_len
     first_tok = row_begin // group
     last_tok = (row_begin + row_count - 1) // group
     hi = ctx + last_tok + 1
     lo = max(0, ctx + first_tok - window + 1) if window else 0
+    if chunk:
+        # What the tile's first token sees bounds the tile from below.
+        lo = max(lo, (ctx + first_tok) // chunk * chunk)
     return lo, hi
 
 
@@ -208,6 +213,8 @@ def _plan_with_arrays(q_lens: Sequence[int], kv_lens: Sequence[int], opt: PlanOp
         lo = np.maximum(0, ctx + row_begin // group - opt.window + 1)
     else:
         lo = np.zeros(total, np.int64)
+    if opt.chunk:
+        lo = np.maximum(lo, (ctx + row_begin // group) // opt.chunk * opt.chunk)
     span = hi - lo
     num_tiles = len(kind_of)
     base_ctas = num_tiles * opt.num_kv_heads
@@ -313,7 +320,7 @@ def plan_attention_plain(
         height = TILE_ROWS[kind]
         for row_begin in range(0, rows, height):
             row_count = min(height, rows - row_begin)
-            lo, hi = _key_range(q_len, kv_len, opt.group, opt.window, row_begin, row_count)
+            lo, hi = _key_range(q_len, kv_len, opt.group, opt.window, row_begin, row_count, opt.chunk)
             tiles.append((kind, seq, row_begin, row_count, lo, hi))
 
     base_ctas = len(tiles) * opt.num_kv_heads
@@ -418,7 +425,7 @@ def plan_anchored(q_lens: Sequence[int], kv_lens: Sequence[int], opt: PlanOption
         out = per_kind.setdefault(kind, [])
         for row_begin in range(0, rows, height):
             row_count = min(height, rows - row_begin)
-            lo, hi = _key_range(q_len, kv_len, opt.group, opt.window, row_begin, row_count)
+            lo, hi = _key_range(q_len, kv_len, opt.group, opt.window, row_begin, row_count, opt.chunk)
             kept = min(max(opt.keep_first, 0), lo)
             count = 2 if (kept > 0 or always_two) else 1
             stride = opt.num_kv_heads * row_count
@@ -505,6 +512,8 @@ def plan_single_tokens(kv_lens: np.ndarray, num_seqs: int, splits: int, opt: Pla
     items[:, 5] = -1
     kv = np.asarray(kv_lens, dtype=np.int64)
     lo = np.maximum(0, kv - opt.window) if opt.window else np.zeros_like(kv)
+    if opt.chunk:
+        lo = np.maximum(lo, (kv - 1) // opt.chunk * opt.chunk)
     if splits == 1:
         items[:n, 0] = np.arange(n)
         items[:n, 2] = opt.group

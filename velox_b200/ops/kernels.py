@@ -166,10 +166,40 @@ def mixers():
     return _mixers
 
 
+_heads = None
+
+
+def heads():
+    """The library of row kernels around attention heads and gated feed-forwards (built at first use)."""
+    global _heads
+    if _heads is None:
+        lib = build.load_heads()
+        lib.vx_norm_shift.argtypes = [
+            _ptr, _c_ll, _c_int, _c_f, _ptr, _ptr, _ptr, _ptr, _c_ll, _ptr, _ptr, _c_int, _ptr, _ptr, _ptr, _c_int,
+            _c_int, _ptr,
+        ]
+        lib.vx_add_rows.argtypes = [_ptr, _ptr, _ptr, _c_int, _c_ll, _ptr]
+        lib.vx_diff_prepare.argtypes = [
+            _ptr, _c_int, _c_ll, _ptr, _c_ll, _ptr, _ptr, _ptr, _ptr, _ptr, _c_f, _ptr, _ptr, _ptr, _c_int, _c_int,
+            _c_int, _c_int, _c_int, _c_int, _c_int, _c_int, _c_ll, _c_int, _ptr, _ptr,
+        ]
+        lib.vx_diff_combine.argtypes = [
+            _ptr, _c_int, _c_ll, _ptr, _c_ll, _ptr, _c_ll, _c_int, _c_int, _c_int, _c_int, _c_f, _c_f, _c_f, _ptr,
+        ]
+        lib.vx_clamped_glu.argtypes = [_ptr, _c_int, _c_ll, _ptr, _c_ll, _c_int, _c_int, _c_f, _c_f, _c_f, _ptr]
+        _heads = lib
+    return _heads
+
+
 def attention_lib(head_dim: int):
     lib = _attention.get(head_dim)
     if lib is None:
         lib = build.load_attention(head_dim)
+        lib.vx_attention_scored.argtypes = [
+            _c_int, _ptr, _ptr, _ptr, _ptr, _ptr, _ptr, _ptr, _ptr, _ptr, _c_int, _ptr, _ptr, _ptr, _ptr, _ptr,
+            _c_int, _c_int, _c_int, _c_int, _c_int, _c_int, _c_ll, _c_int, _c_f, _c_int, _c_int, _c_f, _ptr, _ptr,
+            _c_int, _c_int, _ptr, _c_int, _ptr,
+        ]
         lib.vx_attention.argtypes = [
             _c_int, _ptr, _ptr, _ptr, _ptr, _ptr, _ptr, _ptr, _ptr, _ptr, _c_int, _ptr, _ptr, _ptr, _ptr, _ptr,
             _c_int, _c_int, _c_int, _c_int, _c_int, _c_int, _c_ll, _c_int, _c_f, _c_int, _c_int, _ptr,
@@ -988,6 +1018,11 @@ def attention(
     cluster: int = 1,
     layout_checked: bool = False,
     keep_first: int = 0,
+    softcap: float = 0.0,
+    distance_bias: Optional[tuple] = None,
+    chunk: int = 0,
+    sink_zero: bool = False,
+    row_scale: Optional[torch.Tensor] = None,
 ) -> None:
     """Run ``num_items`` work items (see attention.cu for their layout) of one kernel family.
 
@@ -1001,6 +1036,13 @@ def attention(
     memory.  For the tensor-memory family 2 asks for two CTAs on an SM whatever the grid's size
     (the caller knows that the items' key ranges are long).  ``keep_first`` (with a window): keys
     0 .. keep_first - 1 stay visible to every later query.
+
+    Changes to a score ``s = (q . k) * softmax_scale`` before the softmax (not in the
+    tensor-memory family): ``row_scale`` (float32 table over positions): ``s *= row_scale[pos]``;
+    ``softcap`` c > 0: ``s = c tanh(s / c)``; ``distance_bias`` (r1, r2), float32 per query head:
+    ``s -= r1 ln(1 + r2 (pos - n))``; ``chunk`` c > 0: a query at ``pos`` sees keys from
+    ``floor(pos / c) * c`` on; ``sink_zero``: one more term of score 0 and no value in every
+    row's denominator (layers without window or chunk).
     """
     want = torch.float32 if kind == ATTN_F32 else torch.bfloat16
     _need(q, want, "q")
@@ -1022,15 +1064,26 @@ def attention(
             _need(split_counters, torch.int32, "split_counters")
             _need(merge_items, torch.int32, "merge_items")
     lib = attention_lib(head_dim)
+    r1 = r2 = None
+    if distance_bias is not None:
+        r1, r2 = distance_bias
+        _need(r1, torch.float32, "distance_bias r1")
+        _need(r2, torch.float32, "distance_bias r2")
+        if r1.numel() != num_heads or r2.numel() != num_heads:
+            raise ValueError("the distance bias needs two numbers per query head")
+    if row_scale is not None:
+        _need(row_scale, torch.float32, "row_scale")
     _check(
-        lib.vx_attention(kind, _p(q), _p(out), _p(k_cache), _p(v_cache), _p(block_tables),
-                         _p(q_start), _p(q_len), _p(kv_len), _p(items), num_items,
-                         _p(status if status is not None else _attention_status()),
-                         _p(partial_o), _p(partial_lse), _p(merge_items), _p(split_counters),
-                         q.shape[1], out.shape[1],
-                         block_tables.shape[1], num_kv_heads, num_heads // num_kv_heads,
-                         k_cache.shape[1], k_cache.shape[0], int(window or 0), float(softmax_scale),
-                         int(cluster), int(keep_first or 0), _stream()),
+        lib.vx_attention_scored(kind, _p(q), _p(out), _p(k_cache), _p(v_cache), _p(block_tables),
+                                _p(q_start), _p(q_len), _p(kv_len), _p(items), num_items,
+                                _p(status if status is not None else _attention_status()),
+                                _p(partial_o), _p(partial_lse), _p(merge_items), _p(split_counters),
+                                q.shape[1], out.shape[1],
+                                block_tables.shape[1], num_kv_heads, num_heads // num_kv_heads,
+                                k_cache.shape[1], k_cache.shape[0], int(window or 0), float(softmax_scale),
+                                int(cluster), int(keep_first or 0), float(softcap or 0.0), _p(r1), _p(r2),
+                                int(chunk or 0), 1 if sink_zero else 0, _p(row_scale),
+                                0 if row_scale is None else row_scale.numel(), _stream()),
         "attention",
     )
 
@@ -1532,3 +1585,78 @@ def table_experts_library(h, ids, fed, table, w_up, w_down, route, run_ends, a_r
     _check(mixers().vx_gather_pairs(_p(down), _p(route), places, top, width, _p(resid), num_tokens, _stream()),
            "gather_pairs")
     return True
+
+
+# ------------------------------------------------------------------------------------------
+# The ``heads`` library.
+def norm_shift(resid, weight, eps, out, num_tokens, q_start, q_len, seq_slots, num_seqs, weight2=None, out2=None,
+               shift=None, state=None) -> None:
+    """``out = h`` with ``h = resid / rms(resid) * weight`` per row, or, with ``shift`` (float32
+    [width]) and ``state`` (float32, a row per state slot), ``h + (h_before - h) * shift`` where
+    ``h_before`` is the same norm of the request's previous token (from the row above, or from
+    the state row for a portion's first row; the portion's last ``h`` goes into the state row).
+    ``weight2`` / ``out2``: a second output ``resid / rms(resid) * weight2`` from the same
+    statistic."""
+    _need(resid, torch.float32, "resid")
+    _need(weight, torch.float32, "weight")
+    width = resid.shape[1]
+    if weight2 is not None:
+        _need(weight2, torch.float32, "weight2")
+        _need(out2, out.dtype, "out2")
+    if shift is not None:
+        _need(shift, torch.float32, "shift")
+        if state is None or state.dtype != torch.float32 or state.stride(-1) != 1 or state.shape[1] < width:
+            raise ValueError("token shift needs a float32 state row of at least the width per slot")
+    _check(heads().vx_norm_shift(_p(resid), resid.stride(0), width, float(eps), _p(weight), _p(weight2), _p(shift),
+                                 _p(state), 0 if state is None else state.stride(0), _p(out), _p(out2),
+                                 _code(out.dtype), _p(q_start), _p(q_len), _p(seq_slots), int(num_seqs),
+                                 int(num_tokens), _stream()),
+           "norm_shift")
+
+
+def add_rows(resid, a, b, num_tokens) -> None:
+    """resid[:num_tokens] += a (+ b), float32 sums; a and b in the compute dtype, same row width."""
+    _need(resid, torch.float32, "resid")
+    _need(a, a.dtype, "a")
+    if b is not None:
+        _need(b, a.dtype, "b")
+    _check(heads().vx_add_rows(_p(resid), _p(a), _p(b), _code(a.dtype), num_tokens * resid.shape[1], _stream()),
+           "add_rows")
+
+
+def diff_prepare(proj, qbuf, positions, cos, sin, q_norm, k_norm, eps, slots, k_cache, v_cache, num_tokens,
+                 num_heads, num_kv_heads, dim, vdim, head_dim, rotary_dim, status) -> None:
+    """Differential attention's way into the attention kernels (see csrc/heads.cu): per (head,
+    map) RMS norm and rotation of q and k; q into ``qbuf`` [T, 2 H * head_dim], k of both maps side
+    by side and v into their cache rows."""
+    stride = _pitched(proj, "proj")
+    write = k_cache is not None
+    if rotary_dim > 0:
+        _need(cos, torch.float32, "cos")
+        _need(sin, torch.float32, "sin")
+        if cos.shape[1] != rotary_dim // 2:
+            raise ValueError("cos/sin tables do not match the rotary width")
+    _check(heads().vx_diff_prepare(
+        _p(proj), _code(proj.dtype), stride, _p(qbuf), qbuf.stride(0), _p(positions),
+        _p(cos) if rotary_dim > 0 else None, _p(sin) if rotary_dim > 0 else None, _p(q_norm), _p(k_norm),
+        float(eps), _p(slots), _p(k_cache), _p(v_cache), num_tokens, num_heads, num_kv_heads, dim, vdim,
+        head_dim, rotary_dim, cos.shape[0] if rotary_dim > 0 else 0,
+        k_cache.shape[0] * k_cache.shape[1] if write else 0, 1 if write else 0, _p(status), _stream()),
+        "diff_prepare")
+
+
+def diff_combine(attn, gate, out, num_tokens, num_heads, vdim, head_dim, lam, out_scale, eps) -> None:
+    """``out[t, h] = unit_rms(a1 - lam * a2) * out_scale * sigmoid(gate[t, h])`` over a head's
+    ``vdim`` values, a1 / a2 the two maps' rows of ``attn`` [T, 2 H * head_dim]."""
+    _check(heads().vx_diff_combine(
+        _p(attn), _code(attn.dtype), attn.stride(0), _p(gate), 0 if gate is None else _pitched(gate, "gate"),
+        _p(out), out.stride(0), num_tokens, num_heads, vdim, head_dim, float(lam), float(out_scale), float(eps),
+        _stream()), "diff_combine")
+
+
+def clamped_glu(gate_up, out, num_tokens, inner, limit, alpha, up_shift) -> None:
+    """``out = g * sigmoid(alpha * g) * (u + up_shift)`` with ``g = min(gate, limit)``, ``u =
+    clamp(up, -limit, limit)`` (no clamps when ``limit`` is 0); gate columns first in ``gate_up``."""
+    _check(heads().vx_clamped_glu(_p(gate_up), _code(gate_up.dtype), _pitched(gate_up, "gate_up"), _p(out),
+                                  out.stride(0), num_tokens, inner, float(limit or 0.0), float(alpha),
+                                  float(up_shift), _stream()), "clamped_glu")

@@ -1,5 +1,5 @@
 """Parts a model is put together from.  Importing the package registers the built-in ones."""
-from . import attention, block, io, latent_attention, mlp, norms, recurrent, rope  # noqa: F401
+from . import attention, block, differential_attention, io, latent_attention, mlp, norms, recurrent, rope  # noqa: F401
 from .base import (
     CacheNeeds,
     FeedForward,

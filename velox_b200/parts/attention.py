@@ -14,6 +14,13 @@ first ``keep_first`` keys; a learned sink per head in the softmax denominator (`
 per head on the heads' outputs, ``sigmoid(W_g x)`` (``head_gate``: its rows ride along behind
 q | k | v in the one projection).  Such a part takes its matrices as ``q.weight``, ``k.weight``,
 ``v.weight`` (and biases) instead of one ``qkv.weight``.
+
+Changes to the scores, made inside the attention kernels: ``distance_bias`` (weights ``bias_r1``,
+``bias_r2``, one number each per query head): ``r1 ln(1 + r2 (i - j))`` is taken off the score of
+query i and key j; ``sink_zero``: one more term of score 0 and no value in every softmax
+denominator (without a window); a position part with a ``row_scale`` table (``log_temperature``)
+multiplies a query's scores by a number that depends on its position.  Layers with any of these
+run on the float32, wide and narrow kernel families.
 """
 from __future__ import annotations
 
@@ -59,6 +66,14 @@ class Attention(Mixer):
         # Rows finished by the merge kernel: that is where a sink and the kept first keys come in.
         self.anchored = self.sink is not None or self.keep_first > 0
         self.head_gate = bool(params.get("head_gate", False))
+        self.sink_zero = bool(params.get("sink_zero", False))
+        if self.sink_zero and (self.window or self.sink is not None):
+            raise ValueError("attention: sink_zero goes with neither a window nor a learned sink")
+        self.distance_bias = None
+        if params.get("distance_bias", False):
+            self.distance_bias = (self.expect("bias_r1", (self.num_heads,)), self.expect("bias_r2", (self.num_heads,)))
+        self.row_scale = getattr(position, "row_scale", None)
+        self.scored = self.sink_zero or self.distance_bias is not None or self.row_scale is not None
         self.b_qkv = None
         self.b_qkv_lowp = None
         if "qkv.weight" in weights:
@@ -130,6 +145,9 @@ class Attention(Mixer):
 
     def attention_signature(self):
         base = (self.num_kv_heads, self.num_heads // self.num_kv_heads, self.window, self.head_dim)
+        if self.scored:
+            # Changed scores: no tensor-memory family in the layout.
+            return base + (self.keep_first, self.anchored, (("wide_on_tensor_memory", False),))
         return base + (self.keep_first, True) if self.anchored else base
 
     # The input is used by the QKV projection only, which can make the norm itself.
@@ -168,7 +186,8 @@ class Attention(Mixer):
                 cluster=(plan.cluster if kind == kernels.ATTN_BF16_NARROW else
                          getattr(plan, "tc_ctas_per_sm", 1) if kind == kernels.ATTN_BF16_TC else 1),
                 layout_checked=getattr(plan, "checked", False),
-                keep_first=self.keep_first,
+                keep_first=self.keep_first, distance_bias=self.distance_bias, sink_zero=self.sink_zero,
+                row_scale=self.row_scale,
             )
         if hasattr(plan, "checked"):
             plan.checked = True

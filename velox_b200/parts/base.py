@@ -57,6 +57,9 @@ class PagedCacheSpec:
     values_in_keys: bool = False
     # With a window: the first ``keep_first`` keys stay visible (and cached) for ever.
     keep_first: int = 0
+    # A chunked mask (0: none): a query sees the keys of its own chunk of ``chunk`` positions,
+    # counted from 0, so the pages of earlier chunks can be given back.
+    chunk: int = 0
 
 
 @dataclass(frozen=True)
@@ -71,6 +74,9 @@ class StateSpec:
 class CacheNeeds:
     paged: Optional[PagedCacheSpec] = None
     state: Optional[StateSpec] = None
+    # A state row per request for the block arrangement around the mixer (what a token shift
+    # remembers of the previous token), declared by the block's ``state_needs()``.
+    block_state: Optional[StateSpec] = None
 
 
 class PendingNorm:

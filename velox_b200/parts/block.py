@@ -162,21 +162,65 @@ class PostNormBlock:
 
 @register_part("block", "parallel")
 class ParallelBlock:
-    """One norm, and both sublayers read its output:  ``h = norm(x);  x <- x + (mixer(h) +
-    feed_forward(h))``.  A layer may have no feed-forward.  The sums are float32: a part adds its
-    product into the stream itself where it can (``ctx.residual``), what it returns instead is
-    added here, and the last product may stay pending for the next norm to add."""
+    """Both sublayers read the same rows x:  ``x <- x + (mixer(norm_a(x)) + feed_forward(norm_b(x)))``.
+    With one norm (``norms["input"]`` alone) both read its output; with ``norms["feed_forward"]``
+    as well, each sublayer has its own norm of the same x.  A layer may have no feed-forward.
+    The sums are float32: a part adds its product into the stream itself where it can
+    (``ctx.residual``), what it returns instead is added here, and the last product may stay
+    pending for the next norm to add.
 
-    def __init__(self, mixer, feed_forward, norms, params=None) -> None:
+    ``token_shift`` (block weight ``shift`` [width]): the mixer does not read ``h_t = norm_a(x_t)``
+    but ``h_t + (h_(t-1) - h_t) * shift`` with the request's previous token's h (as the norm
+    made it; zeros before the first token).  The last h of a request is a float32 state row of
+    the block.  Norms and shift are one kernel, which reads x once.
+    """
+
+    def __init__(self, mixer, feed_forward, norms, params=None, weights=None, dtype=None, device=None) -> None:
+        params = dict(params or {})
         self.mixer = mixer
         self.feed_forward = feed_forward
         self.norm = norms["input"]
+        self.norm_feed_forward = norms.get("feed_forward")
+        self.shift = None
+        if params.get("token_shift", False):
+            if weights is None or "shift" not in weights:
+                raise ValueError("a block with token_shift needs the weight 'shift'")
+            self.shift = weights["shift"]
+            if tuple(self.shift.shape) != (self.norm.size,):
+                raise ValueError(f"the weight 'shift' has shape {tuple(self.shift.shape)}, expected ({self.norm.size},)")
+        self.two_outputs = self.norm_feed_forward is not None and feed_forward is not None
+        if self.two_outputs and (self.norm_feed_forward.eps != self.norm.eps or self.norm_feed_forward.center
+                                 or self.norm.center):
+            raise ValueError("a parallel block's two norms are RMS norms with one eps")
+        if self.shift is not None or self.two_outputs:
+            kernels.heads()
+
+    def state_needs(self):
+        """A row of the model's width per request: the previous token's normed input."""
+        if self.shift is None:
+            return None
+        from .base import StateSpec
+
+        return StateSpec((self.norm.size,))
 
     def forward(self, hidden: HiddenState, ctx, cache) -> None:
         T = ctx.num_tokens
         ws = ctx.workspace
-        normed = ws.get("block.normed", (ws.max_tokens, hidden.resid.shape[1]), self.mixer.dtype)
-        self.norm.forward(hidden.resid, hidden.delta, normed, T)
+        width = hidden.resid.shape[1]
+        normed = ws.get("block.normed", (ws.max_tokens, width), self.mixer.dtype)
+        for_feed_forward = normed
+        if self.shift is None and not self.two_outputs:
+            self.norm.forward(hidden.resid, hidden.delta, normed, T)
+        else:
+            if hidden.delta is not None:
+                kernels.add_rows(hidden.resid, hidden.delta, None, T)
+            if self.two_outputs:
+                for_feed_forward = ws.get("block.normed_b", (ws.max_tokens, width), self.mixer.dtype)
+            kernels.norm_shift(
+                hidden.resid, self.norm.weight, self.norm.eps, normed, T, ctx.q_start, ctx.q_len, ctx.seq_slots,
+                ctx.num_seqs, weight2=self.norm_feed_forward.weight if self.two_outputs else None,
+                out2=for_feed_forward if self.two_outputs else None, shift=self.shift,
+                state=cache.block_state if self.shift is not None else None)
         hidden.delta = None
         ctx.residual = hidden.resid
         ctx.residual_mirror = None
@@ -186,6 +230,9 @@ class ParallelBlock:
             hidden.delta = mixed
         else:
             if mixed is not None:
-                kernels.residual_add(hidden.resid, mixed, T)
-            hidden.delta = self.feed_forward.forward(normed, ctx)
+                if self.shift is None and not self.two_outputs:
+                    kernels.residual_add(hidden.resid, mixed, T)
+                else:
+                    kernels.add_rows(hidden.resid, mixed, None, T)
+            hidden.delta = self.feed_forward.forward(for_feed_forward, ctx)
         ctx.residual = None

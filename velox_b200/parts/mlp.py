@@ -209,6 +209,62 @@ class DenseAct(FeedForward):
         return out
 
 
+@register_part("feed_forward", "clamped_glu")
+class ClampedGLU(FeedForward):
+    """A gated feed-forward with clamps and biases:
+
+        g = min(W_g x + b_g, limit);   u = clamp(W_u x + b_u, -limit, limit)
+        y = g * sigmoid(alpha * g) * (u + up_shift);   out = W_d y + b_d
+
+    ``gate_up.weight`` holds the gate rows first, then the up rows (and ``gate_up.bias`` alike);
+    ``limit`` 0 means no clamps; ``alpha`` and ``up_shift`` default to 1 and 0, which is SwiGLU.
+    The activation is float32.  The inner width need not be a multiple of anything: both halves
+    are padded with rows of zeros to a multiple of eight, which produce y = 0."""
+
+    takes_padded_steps = True
+
+    def __init__(self, params, weights, dtype, device) -> None:
+        super().__init__(params, weights, dtype, device)
+        self.hidden_size = E = int(params["hidden_size"])
+        self.intermediate_size = F = int(params["intermediate_size"])
+        self.limit = float(params.get("limit") or 0.0)
+        self.alpha = float(params.get("alpha", 1.0))
+        self.up_shift = float(params.get("up_shift", 0.0))
+        if self.limit < 0.0:
+            raise ValueError(f"clamped_glu: limit={self.limit} must not be negative")
+        w = self.expect("gate_up.weight", (2 * F, E))
+        b = self.expect("gate_up.bias", (2 * F,)) if params.get("biases", True) else None
+        self.inner = Fp = -(-F // 8) * 8
+        self.w_gate_up = torch.cat([_pad_to(w[:F], 0), _pad_to(w[F:], 0)]).contiguous()
+        self.b_gate_up = None if b is None else torch.cat([_pad_to(b[:F], 0), _pad_to(b[F:], 0)]).contiguous()
+        self.w_down = _pad_to(self.expect("down.weight", (E, F)), 1)
+        self.b_down = self.expect("down.bias", (E,)) if params.get("biases", True) else None
+        lowp = dtype != torch.float32
+        self.b_gate_up_lowp = self.b_gate_up.to(dtype) if lowp and self.b_gate_up is not None else None
+        self.b_down_lowp = self.b_down.to(dtype) if lowp and self.b_down is not None else None
+        self.weights.pop("gate_up.weight", None)
+        kernels.heads()
+
+    def forward(self, x, ctx):
+        T = ctx.num_tokens
+        ws = ctx.workspace
+        if hasattr(x, "materialize"):
+            x = x.materialize()
+        Fp = self.inner
+        gate_up = ws.get(f"clamped_glu.gate_up{2 * Fp}", (ws.max_tokens, 2 * Fp), self.dtype)
+        linear(x, self.w_gate_up, self.b_gate_up, gate_up, T, self.b_gate_up_lowp, status=ctx.status)
+        act = ws.get(f"clamped_glu.act{Fp}", (ws.max_tokens, Fp), self.dtype)
+        kernels.clamped_glu(gate_up, act, T, Fp, self.limit, self.alpha, self.up_shift)
+        if (ctx.residual is not None and ctx.status is not None and self.dtype != torch.float32
+                and use_tensor_core_kernel(act, self.w_down, T)):
+            # Few tokens: the down projection (and its bias) goes straight into the float32 stream.
+            linear(act, self.w_down, self.b_down, ctx.residual, T, status=ctx.status, accumulate=True)
+            return None
+        out = ws.get("feed_forward.out", (ws.max_tokens, self.hidden_size), self.dtype)
+        linear(act, self.w_down, self.b_down, out, T, self.b_down_lowp, status=ctx.status)
+        return out
+
+
 def _lowered(sums: torch.Tensor, ws, dtype, num_rows: int, name: str) -> torch.Tensor:
     """float32 rows in the compute dtype (for a block that has offered no stream to add into)."""
     if dtype == torch.float32:

@@ -2,6 +2,8 @@
 src/decoder_layer.py:49,54)."""
 from __future__ import annotations
 
+import torch
+
 from ..ops import kernels
 from .base import Norm, PendingNorm
 from .registry import register_part
@@ -9,13 +11,18 @@ from .registry import register_part
 
 @register_part("norm", "rms")
 class RMSNorm(Norm):
-    """``out = v * rsqrt(mean(v^2) + eps) * weight`` with ``v = resid + delta``, in float32."""
+    """``out = v * rsqrt(mean(v^2) + eps) * weight`` with ``v = resid + delta``, in float32.
+    ``weight_offset`` c: the stored weight lies around zero and the factor is ``c + weight``
+    (added once, in float32, when the part is built)."""
 
     def __init__(self, params, weights, dtype, device) -> None:
         super().__init__(params, weights, dtype, device)
         self.size = int(params["size"])
         self.eps = float(params["eps"])
         self.weight = self.expect("weight", (self.size,))
+        offset = float(params.get("weight_offset", 0.0))
+        if offset != 0.0:
+            self.weight = (self.weight.to(torch.float32) + offset).contiguous()
 
     def forward(self, resid, delta, out, num_rows, rows=None, write_resid=True):
         kernels.add_rmsnorm(resid, delta, self.weight, self.eps, out, num_rows, rows, write_resid)

@@ -28,14 +28,18 @@ class RotaryHalf(PositionEncoding):
             raise ValueError(
                 f"rotary_dim={self.rotary_dim} must be even and within head_dim={self.head_dim}"
             )
-        exponent = torch.arange(0, self.rotary_dim, 2, dtype=torch.float32) / self.rotary_dim
+        # ``angles``: "float32" forms position * frequency in float32 (the reference's tables);
+        # "float64" forms it in float64 and rounds the cosine and sine once.
+        precise = params.get("angles", "float32") == "float64"
+        work = torch.float64 if precise else torch.float32
+        exponent = torch.arange(0, self.rotary_dim, 2, dtype=work) / self.rotary_dim
         inv_freq = 1.0 / (self.theta ** exponent)
-        positions = torch.arange(self.max_position, dtype=torch.float32)
+        positions = torch.arange(self.max_position, dtype=work)
         if self.scaling_factor != 1.0:
             positions = positions / self.scaling_factor
         angles = torch.outer(positions, inv_freq)
-        self.cos = angles.cos().to(device).contiguous()
-        self.sin = angles.sin().to(device).contiguous()
+        self.cos = angles.cos().to(torch.float32).to(device).contiguous()
+        self.sin = angles.sin().to(torch.float32).to(device).contiguous()
 
     def rotate_and_store(self, qkv, ctx, slots, k_cache, v_cache, num_heads, num_kv_heads):
         kernels.rope_cache_write(
@@ -65,6 +69,25 @@ class NoPosition(PositionEncoding):
             qkv, ctx.positions, None, None, slots, k_cache, v_cache, ctx.num_tokens,
             num_heads, num_kv_heads, self.head_dim, 0, ctx.status,
         )
+
+
+@register_part("position", "log_temperature")
+class LogTemperature(NoPosition):
+    """No rotation; instead the scores of the query at position p are multiplied by
+    ``1 + coef * ln(floor((p + 1) / every) + 1)``.  The part owns the float32 table ``row_scale``
+    [max_position] (formed in float64, rounded once), which the attention kernels apply to a
+    row's scores; q itself is left as the projection made it."""
+
+    def __init__(self, params, weights, dtype, device) -> None:
+        super().__init__(params, weights, dtype, device)
+        self.coef = float(params["coef"])
+        self.every = int(params["every"])
+        self.max_position = int(params["max_position"])
+        if self.every < 1:
+            raise ValueError(f"log_temperature: every={self.every} must be at least 1")
+        p = torch.arange(self.max_position, dtype=torch.float64)
+        table = 1.0 + self.coef * torch.log(torch.floor((p + 1.0) / self.every) + 1.0)
+        self.row_scale = table.to(torch.float32).to(device).contiguous()
 
 
 @register_part("position", "rotary_interleaved")

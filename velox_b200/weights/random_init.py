@@ -9,7 +9,7 @@ Every tensor is drawn from its own generator, keyed by (seed, tensor name), so a
 values do not depend on which other tensors exist or on the order they are made in.  Matrices
 and biases are N(0, std); norm weights are 1 + N(0, std) so that a missing norm multiply shows;
 the weights of a weighted sum are 1/n + N(0, std); an integer table gets rows of different
-numbers below its bound.
+numbers below its bound; a tensor may ask for a uniform range of its own.
 """
 from __future__ import annotations
 
@@ -46,6 +46,13 @@ def random_tensor(source: TensorSource, seed: int, std: float, dtype: torch.dtyp
         rows, picks = source.shape
         order = torch.rand((rows, bound), generator=generator).argsort(dim=1)
         return order[:, :picks].to(torch.int32).contiguous()
+    if source.init.startswith("uniform:"):
+        # Numbers of a fixed range whatever ``std`` is (a mixing weight between 0 and 1, a
+        # positive slope): "uniform:<low>:<high>".
+        _, low, high = source.init.split(":")
+        values = torch.empty(source.shape, dtype=torch.float32)
+        values.uniform_(float(low), float(high), generator=generator)
+        return values.to(dtype)
     values = torch.empty(source.shape, dtype=torch.float32)
     values.normal_(0.0, std, generator=generator)
     if source.init == "one_plus_normal":
