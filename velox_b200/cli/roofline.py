@@ -113,13 +113,57 @@ def _redalix_layer(entry: Dict, width: int, tokens: int, batch: int, context: in
     return 2 * weights, cache, flops
 
 
+def _is_lizizen(config_json: Dict) -> bool:
+    return config_json.get("architecture") == "Lizizen" or "Lizizen" in (config_json.get("architectures") or [])
+
+
+def _lizizen_layer(entry: Dict, width: int, tokens: int, batch: int, context: int):
+    """(bytes of weights read, bytes of cache and state touched, operations) of one Lizizen layer
+    for ``tokens`` new tokens of each of ``batch`` sequences behind ``context`` keys.  A cached
+    row is as wide as the attention kernels' head: both maps' keys side by side for
+    ``attention_2``, whose chunked mask bounds the keys a token reads and whose two maps are two
+    score products over one set of values."""
+    m = entry["mixer"]
+    rows = batch * tokens
+    maps = 2 if entry["type"] == "attention_2" else 1
+    head = -(-max(maps * m["dim"], m["vdim"]) // 16) * 16
+    weights = width * (m["heads"] * maps * m["dim"] + m["kv_heads"] * (maps * m["dim"] + m["vdim"])) + m["heads"] * m["vdim"] * width
+    if maps == 2:
+        weights += m["heads"] * m["vdim"] * width  # the output gate
+    reach = (m.get("mask") or {}).get("size") or (context + tokens)
+    if tokens <= 4096:
+        if maps == 2 and m.get("mask"):
+            pairs = sum((context + i) % reach + 1 for i in range(tokens))
+        else:
+            pairs = sum(context + i + 1 for i in range(tokens))
+    else:
+        pairs = tokens * min(reach, context + tokens) / 2
+    cache = batch * min(context + tokens, reach + tokens) * 2 * m["kv_heads"] * head * 2
+    cache += batch * width * 4 * 2  # the shift's row, read and written
+    flops = 2.0 * rows * weights + 4.0 * batch * pairs * maps * m["heads"] * head
+    mlp = entry.get("mlp")
+    if mlp is not None:
+        weights += 3 * mlp["ff"] * width
+        flops += 2.0 * rows * 3 * mlp["ff"] * width
+    return 2 * weights, cache, flops
+
+
+def _listed_layer(config_json: Dict):
+    """The per-layer accounting of a design whose layers differ in kind, or None."""
+    if _is_redalix(config_json):
+        return _redalix_layer
+    if _is_lizizen(config_json):
+        return _lizizen_layer
+    return None
+
+
 def layer_bytes(config_json: Dict, batch: int, context: int) -> Tuple[int, int]:
     """(bytes of one layer's matrices in bfloat16, bytes of ``batch`` x ``context`` cached rows of
     one layer: keys and values, or the latent rows that serve as both), averaged over the layers
     of a configuration that lists them."""
     entries = _latent_layers(config_json)
-    if entries is not None and _is_redalix(config_json):
-        parts = [_redalix_layer(entry, config_json["width"], 1, batch, context) for entry in entries]
+    if entries is not None and _listed_layer(config_json) is not None:
+        parts = [_listed_layer(config_json)(entry, config_json["width"], 1, batch, context) for entry in entries]
         return sum(p[0] for p in parts) // len(parts), sum(p[1] for p in parts) // len(parts)
     if entries is not None:
         width = config_json["width"]
@@ -146,8 +190,8 @@ def layer_flops(config_json: Dict, tokens: int, context: int) -> float:
     (for latent attention: as the engine computes it, scores and sums over the cached rows)."""
     entries = _latent_layers(config_json)
     pairs = tokens * (context + (tokens + 1) / 2.0)
-    if entries is not None and _is_redalix(config_json):
-        return sum(_redalix_layer(entry, config_json["width"], tokens, 1, context)[2] for entry in entries) / len(entries)
+    if entries is not None and _listed_layer(config_json) is not None:
+        return sum(_listed_layer(config_json)(entry, config_json["width"], tokens, 1, context)[2] for entry in entries) / len(entries)
     if entries is not None:
         weights, _ = layer_bytes(config_json, 0, 0)
         attention = 0.0

@@ -1,5 +1,5 @@
-"""Named example configurations of the Qwen2.5 dense family, and of the Peratar and Redalix designs
-at the same widths, as ``config.json`` dictionaries.
+"""Named example configurations of the Qwen2.5 dense family, and of the Peratar, Redalix and Lizizen
+designs at the same widths, as ``config.json`` dictionaries.
 
 They exist for runs with random weights (``--model-size`` of the benchmark command line): no
 checkpoint is needed to time the layer sizes of a published model.  Nothing in the engine
@@ -127,6 +127,44 @@ def _redalix_tiny() -> Dict[str, Any]:
             "max_position_embeddings": 512}
 
 
+def _lizizen(like: str, chunk: int = 1024) -> Dict[str, Any]:
+    """A Lizizen configuration with the width, head counts, layer count, feed-forward width and
+    vocabulary of the named Qwen2.5 size.  Its layers alternate ``attention_2`` and ``attention``.
+    An ``attention`` head is as wide as that model's; an ``attention_2`` head has two maps of half
+    that size and values of the whole size, so both mixers have that model's q, k, v and o
+    matrices (``attention_2`` one more of the size of q, for its gate) and cache as many values
+    per key."""
+    base = MODEL_SIZES[like]
+    width, heads, kv_heads = base["hidden_size"], base["num_attention_heads"], base["num_key_value_heads"]
+    head = base.get("head_dim") or width // heads
+    mlp = {"kind": "dense", "ff": base["intermediate_size"], "limit": 7.0}
+    two_maps = {"heads": heads, "kv_heads": kv_heads, "dim": head // 2, "vdim": head, "scale": (head // 2) ** -0.5,
+                "diff": 0.5, "mask": {"size": chunk}, "rot": {"base": base["rope_theta"], "dims": head // 4},
+                "softcap": 50.0}
+    all_keys = {"heads": heads, "kv_heads": kv_heads, "dim": head, "vdim": head, "scale": head ** -0.5,
+                "q_temp": {"coef": 0.1, "every": 1024}}
+    pattern = [{"type": "attention_2", "mixer": two_maps, "mlp": mlp}, {"type": "attention", "mixer": all_keys, "mlp": mlp}]
+    entries = [copy.deepcopy(pattern[index % len(pattern)]) for index in range(base["num_hidden_layers"])]
+    return {"architecture": "Lizizen", "vocab": base["vocab_size"], "width": width, "norm": {"eps": 1e-6},
+            "layers": entries, "max_position_embeddings": base["max_position_embeddings"]}
+
+
+def _lizizen_tiny() -> Dict[str, Any]:
+    """A tiny Lizizen configuration for smoke runs of the command lines: both mixers, a layer
+    without feed-forward, the first two layers run twice."""
+    layers = [
+        {"type": "attention_2", "mixer": {"heads": 4, "kv_heads": 2, "dim": 16, "vdim": 32, "scale": 0.25, "diff": 0.4,
+                                          "mask": {"size": 24}, "rot": {"base": 10000.0, "dims": 8}, "softcap": 10.0},
+         "mlp": {"kind": "dense", "ff": 160, "limit": 2.0}},
+        {"type": "attention", "mixer": {"heads": 4, "kv_heads": 1, "dim": 32, "vdim": 16, "scale": 0.18,
+                                        "q_temp": {"coef": 0.2, "every": 16}}, "mlp": None},
+        {"type": "attention", "mixer": {"heads": 2, "kv_heads": 2, "dim": 16, "vdim": 16, "scale": 0.25},
+         "mlp": {"kind": "dense", "ff": 96, "limit": 1.0}},
+    ]
+    return {"architecture": "Lizizen", "vocab": 384, "width": 128, "norm": {"eps": 1e-5}, "layers": layers,
+            "loop": {"start": 0, "stop": 2, "times": 2}, "max_position_embeddings": 512}
+
+
 MODEL_SIZES.update({
     "tiny-r": _redalix_tiny(),
     "redalix-0.5b": _redalix("0.5b"),
@@ -137,17 +175,24 @@ MODEL_SIZES.update({
     "peratar-1.5b": _peratar("1.5b"),
     "peratar-3b": _peratar("3b"),
     "peratar-7b": _peratar("7b"),
+    "tiny-l": _lizizen_tiny(),
+    "lizizen-0.5b": _lizizen("0.5b"),
+    "lizizen-1.5b": _lizizen("1.5b"),
+    "lizizen-3b": _lizizen("3b"),
 })
 
 
 def with_layers(config_json: Dict[str, Any], layers: int) -> Dict[str, Any]:
     """The configuration with another number of layers of the same sizes (a list of layers is cut,
-    or repeated from its start with every ``kv_from`` kept at its distance)."""
+    or repeated from its start with every ``kv_from`` kept at its distance; a ``loop`` over the list
+    as it was is dropped)."""
     out = copy.deepcopy(config_json)
     if "layers" not in out:
         out["num_hidden_layers"] = layers
         return out
     given = out["layers"]
+    if layers != len(given):
+        out.pop("loop", None)  # a looped stretch names layers of the list as it was
     entries = []
     for index in range(layers):
         entry = copy.deepcopy(given[index % len(given)])
