@@ -566,7 +566,7 @@ def test_keys_far_away_and_at_the_edges_of_a_chunk(tmp_path, dtype, kind, ask_at
     replayer = make_replayer(folder, dtype, max_tokens=384, page=64)
     rows = replay_one(replayer, "n", tokens, [ask_at, 1, length - ask_at - 1])
     check_logits(rows[lo:hi], ref[lo:hi], dtype, f"{kind} needle at {needle_at}, decoded")
-    rows = replay_one(replayer, "m", tokens, [100, 2, ask_at - 110, 20, length - ask_at - 12])
+    rows = replay_one(replayer, "m", tokens, [100, 2, ask_at - 110, 12, length - ask_at - 4])
     check_logits(rows[lo:hi], ref[lo:hi], dtype, f"{kind} needle at {needle_at}, in portions")
     rows = replay_one(replayer, "w", tokens, [length])
     check_logits(rows[lo:hi], ref[lo:hi], dtype, f"{kind} needle at {needle_at}, whole")
