@@ -1037,6 +1037,14 @@ def test_gemm_bf16_add_chunked(k, status, T, N, K, chunks):
     torch.cuda.synchronize()
     assert (out[:T].double() - want).abs().max().item() <= 2e-5 * want.abs().max().item()
     assert torch.equal(out[T:], start[T:])  # rows past the step are not touched
+    # a bias comes in once, whatever the number of chunks
+    bias = torch.randn(N, generator=gen).cuda()
+    out = start.clone()
+    k.gemm_bf16_add_chunked(x, w, out, T, status, chunks, bias=bias)
+    torch.cuda.synchronize()
+    want = want + bias.double()
+    assert (out[:T].double() - want).abs().max().item() <= 2e-5 * want.abs().max().item()
+    assert torch.equal(out[T:], start[T:])
     assert int(status[0]) == 0
 
 

@@ -107,6 +107,31 @@ def test_clamped_gated_activation(dtype, T, F, limit):
     close(out, want, dtype, "activation")
 
 
+@pytest.mark.parametrize("T,F,K,limit,biased", [(1, 128, 64, 1.5, True), (17, 40, 104, 0.7, True), (8, 8960, 1536, 7.0, True),
+                                                (200, 1000, 256, 0.0, False), (64, 72, 896, 2.0, False)])
+def test_gated_activation_in_the_projection(T, F, K, limit, biased):
+    """The same activation in the epilogue of the tensor-core projection of small steps: gate and
+    up rows of one matrix, their biases, clamps, the slope of the sigmoid and the shift of up."""
+    from velox_b200.ops import kernels
+
+    gen = torch.Generator().manual_seed(F + K)
+    x = torch.randn(T + 2, K, generator=gen).to(torch.bfloat16)
+    w = (1.5 * torch.randn(2 * F, K, generator=gen) / math.sqrt(K)).to(torch.bfloat16)
+    b = torch.randn(2 * F, generator=gen) if biased else None
+    y = x[:T].double() @ w.double().T + (b.double() if biased else 0.0)
+    g, u = y[:, :F].numpy(), y[:, F:].numpy()
+    if limit:
+        g, u = np.minimum(g, limit), np.clip(u, -limit, limit)
+    want = g * plain.sigmoid(1.702 * g) * (u + 1.0)
+    out = torch.full((T + 2, F), 9.0, dtype=torch.bfloat16).cuda()
+    status = torch.zeros(1, dtype=torch.int32).cuda()
+    kernels.gemm_bf16_glu(x.cuda(), w.cuda(), b.cuda() if biased else None, out, T, limit, 1.702, 1.0, status)
+    torch.cuda.synchronize()
+    assert int(status.item()) == 0
+    close(out[:T], want, "bfloat16", "activation in the projection")
+    assert torch.all(out[T:] == 9.0)
+
+
 def plain_changed_attention(q, k_all, v_all, ctx, scale, temp=None, bias=None, sink=False, cap=None, chunk=None):
     """q [n, H, D] at positions ctx .. ctx + n - 1 over keys/values [ctx + n, G, D] (float64 numpy)."""
     n, H, _ = q.shape
@@ -130,7 +155,7 @@ def plain_changed_attention(q, k_all, v_all, ctx, scale, temp=None, bias=None, s
 
 
 def run_changed_attention(dtype, H, G, D, P, seqs, seed, temp=None, bias=False, sink=False, cap=None, chunk=None,
-                          min_split_keys=256, max_cluster=1, target_ctas=296):
+                          min_split_keys=256, max_cluster=1, target_ctas=296, tensor_memory=False, fixed_splits=None):
     from velox_b200.ops import attention_plan as ap
     from velox_b200.ops import kernels as k
 
@@ -171,7 +196,8 @@ def run_changed_attention(dtype, H, G, D, P, seqs, seed, temp=None, bias=False, 
         q_lens, kv_lens,
         ap.PlanOptions(num_kv_heads=G, group=H // G, window=None, use_f32=dtype == torch.float32,
                        min_split_keys=min_split_keys, target_ctas=target_ctas, narrow_max_cluster=max_cluster,
-                       narrow_global_split_keys=min_split_keys, wide_on_tensor_memory=False, chunk=chunk or 0))
+                       narrow_global_split_keys=min_split_keys, wide_on_tensor_memory=tensor_memory, chunk=chunk or 0),
+        fixed_splits=fixed_splits)
     dev = lambda x: torch.as_tensor(x, dtype=torch.int32).cuda()
     out = torch.zeros(T, H * D, dtype=dtype, device="cuda")
     partial_o = torch.zeros(max(plan.partial_rows, 1) * D, device="cuda")
@@ -184,7 +210,7 @@ def run_changed_attention(dtype, H, G, D, P, seqs, seed, temp=None, bias=False, 
                     row_scale=table)
     if len(plan.merge_items):
         k.attention_merge(out, dev(q_start), dev(plan.merge_items), len(plan.merge_items), partial_o, partial_lse,
-                          H, G, D, max_rows=64)
+                          H, G, D, max_rows=max(ap.TILE_ROWS[kind] for kind in plan.items))
     torch.cuda.synchronize()
     return out.view(T, H, D).double().cpu().numpy(), want, plan
 
@@ -232,10 +258,38 @@ def test_changed_scores_with_split_key_ranges(dtype, max_cluster):
     assert np.abs(got - want).max() <= tol * np.abs(want).max()
 
 
+CHANGES = [dict(temp=(0.5, 7), bias=True, sink=True), dict(cap=2.0, chunk=150), dict(chunk=64), dict(cap=5.0),
+           dict(bias=True), dict(sink=True, temp=(0.3, 100)), dict(chunk=1), dict(chunk=1000, cap=30.0)]
+
+
+@pytest.mark.parametrize("change", range(len(CHANGES)))
+@pytest.mark.parametrize("H,G,D,P", [(8, 2, 64, 16), (12, 2, 128, 16), (4, 4, 128, 64), (6, 1, 64, 8)])
+def test_changed_scores_on_the_tensor_memory_family(H, G, D, P, change):
+    """The same changes where long portions run on tcgen05 tiles of 128 rows x 64 keys: rows of
+    one tile in different chunks, tiles wholly before a row's chunk, the term of score 0 as the
+    start of a row's running sum, key ranges cut into several items."""
+    from velox_b200.ops import attention_plan as ap
+    from velox_b200.ops import kernels
+
+    if not kernels.attention_has_tc(D):
+        pytest.skip("no tensor-memory family for this head size")
+    seqs = MIXED + [(300, 0), (200, 500), (40, 140), (129, 1), (64, 64)]
+    got, want, plan = run_changed_attention(torch.bfloat16, H, G, D, P, seqs, seed=H + D + change, tensor_memory=True,
+                                            **CHANGES[change])
+    assert len(plan.items.get(ap.KIND_BF16_TC, ())) > 0
+    assert np.abs(got - want).max() <= 2.5e-2 * np.abs(want).max()
+    if change < 2:
+        got, want, plan = run_changed_attention(torch.bfloat16, H, G, D, P, [(130, 900), (256, 1100), (1, 700)], seed=change,
+                                                tensor_memory=True, fixed_splits=3, **CHANGES[change])
+        assert len(plan.items.get(ap.KIND_BF16_TC, ())) > 0 and len(plan.merge_items) > 0
+        assert np.abs(got - want).max() <= 2.5e-2 * np.abs(want).max()
+
+
 @pytest.mark.parametrize("dtype", list(DTYPES))
 @pytest.mark.parametrize("H,G,dim,vdim,D,rot", [(4, 2, 16, 24, 32, 8), (3, 3, 12, 20, 32, 12), (1, 1, 20, 12, 48, 0),
                                                 (4, 1, 128, 96, 256, 64), (6, 2, 10, 6, 32, 4)])
-def test_differential_attention_ends(dtype, H, G, dim, vdim, D, rot):
+@pytest.mark.parametrize("pad", [5, 0])
+def test_differential_attention_ends(dtype, H, G, dim, vdim, D, rot, pad):
     """Before the attention kernels: norm and rotation per head and map, the maps' places in a
     query row and in a cached key row, values in their pages.  After them: a1 - lambda a2, unit
     RMS, the factor and the gate."""
@@ -245,7 +299,8 @@ def test_differential_attention_ends(dtype, H, G, dim, vdim, D, rot):
     gen = torch.Generator().manual_seed(dim + vdim)
     T, P, pages, eps = 11, 4, 9, 1e-5
     qw, kw, vw = 2 * H * dim, 2 * G * dim, G * vdim
-    proj = torch.randn(T, qw + kw + vw + H * vdim + 5, generator=gen).to(dt)
+    # with pad 0 the rows are 16-byte multiples where the sizes allow it (the kernels' wide accesses)
+    proj = torch.randn(T, qw + kw + vw + H * vdim + pad, generator=gen).to(dt)
     positions = torch.tensor([0, 1, 2, 3, 40, 41, 7, 99, 5, 6, 63], dtype=torch.int32)
     slots = torch.tensor([4, 5, 6, 7, 20, 21, 9, -1, 30, 31, 35], dtype=torch.int32)
     q_norm, k_norm = 1 + 0.3 * torch.randn(dim, generator=gen), 1 + 0.3 * torch.randn(dim, generator=gen)

@@ -94,8 +94,7 @@ struct AttnArgs {
   // Narrow bf16 family: CTAs of a thread-block cluster that share one work item (1, 2, 4, 8).
   int cluster;
   float scale_log2;  // softmax scale * log2(e)
-  // Changes to a score before the softmax (float32, wide and narrow families; the launcher
-  // refuses them for the tensor-memory family).  With s = (q . k) * scale:
+  // Changes to a score before the softmax (every family).  With s = (q . k) * scale:
   //   softcap > 0:  s <- softcap * tanh(s / softcap)
   //   bias_r1/r2 :  s <- s - r1[h] * ln(1 + r2[h] * (pos - n)), h the query head (null: none)
   //   chunk > 0  :  a row at position pos sees key n only if n >= (pos / chunk) * chunk
@@ -2000,7 +1999,9 @@ __global__ void __launch_bounds__(TC_THREADS, TC_STAGES == 2 ? 2 : 1) attn_tc_ke
 
   // Row state of the softmax threads (valid for warps 0-3).
   const int r = (int)threadIdx.x;  // row of the tile, TMEM lane
-  float m_ref = -CUDART_INF_F, m_true = -CUDART_INF_F, l = 0.f;
+  // A sink of score 0 starts the running sum of the item that begins at key 0 (see AttnArgs).
+  const bool sink_here = a.sink_zero != 0 && kv_begin == 0;
+  float m_ref = sink_here ? 0.f : -CUDART_INF_F, m_true = m_ref, l = sink_here ? 1.f : 0.f;
   bool failed = false;
 
   if (warp == 4) {
@@ -2111,7 +2112,19 @@ __global__ void __launch_bounds__(TC_THREADS, TC_STAGES == 2 ? 2 : 1) attn_tc_ke
     }
     const int pos = r < row_count ? ctx + (row_begin + r) / a.group : -1;
     // The keys this row sees are vis_lo <= n < vis_lo + vis_span (none for a row past the end).
-    const int vis_lo = max(kv_begin, a.window > 0 ? pos - a.window + 1 : 0);
+    const int vis_lo = max(max(kv_begin, a.window > 0 ? pos - a.window + 1 : 0), chunk_start(pos, a.chunk));
+    // Changed scores (see AttnArgs) are formed in natural units: the row's factor, the cap, the
+    // distance bias of the row's head; the exponent's multiply-add then carries log2(e) alone.
+    const bool mods = has_score_mods(a);
+    const float sl2 = mods ? 1.4426950408889634f : a.scale_log2;
+    const float rs = mods ? row_scale_of(a, pos) : 1.0f;
+    float r1ln2 = 0.f, r2 = 0.f;
+    if (a.bias_r1 != nullptr && r < row_count) {
+      const int head = kvh * a.group + (row_begin + r) % a.group;
+      r1ln2 = a.bias_r1[head] * 0.6931471805599453f;
+      r2 = a.bias_r2[head];
+    }
+    const float rcap = a.softcap > 0.f ? rs * 2.885390081777927f / a.softcap : 0.f;  // exp(2 s / cap) as a power of two
     const unsigned vis_span = pos < 0 ? 0u : (unsigned)max(0, min(kv_end, pos + 1) - vis_lo);
     // The kept first keys it sees besides: kv_begin <= n < kv_begin + keep_span.
     const unsigned keep_span = (pos < 0 || a.keep_first <= 0)
@@ -2150,8 +2163,26 @@ __global__ void __launch_bounds__(TC_THREADS, TC_STAGES == 2 ? 2 : 1) attn_tc_ke
       TC_PHASE(1);  // the scores into registers
       // Most tiles lie wholly inside what every row of the warp may see: no masks then.  The
       // scores stay unscaled; the scale goes into the exponent's multiply-add.
-      const bool row_sees_all = pos >= 0 && n0 >= kv_begin && n0 + B_BN <= kv_end && n0 + B_BN - 1 <= pos &&
-                                (a.window <= 0 || n0 > pos - a.window);
+      if (mods) {
+        if (a.softcap > 0.f) {
+#pragma unroll
+          for (int i = 0; i < B_BN; ++i) {
+            const float e = fast_exp2(s[i] * rcap);
+            s[i] = a.softcap * (1.0f - __fdividef(2.0f, e + 1.0f));
+          }
+        } else {
+#pragma unroll
+          for (int i = 0; i < B_BN; ++i) s[i] *= rs;
+        }
+        if (r1ln2 != 0.f) {
+          // 1 + r2 (pos - n0 - i), at least 1: keys ahead of the row are masked below.
+          const float at0 = fmaf(r2, (float)(pos - n0), 1.0f);
+#pragma unroll
+          for (int i = 0; i < B_BN; ++i)
+            s[i] = fmaf(-r1ln2, __log2f(fmaxf(fmaf(-r2, (float)i, at0), 1.0f)), s[i]);
+        }
+      }
+      const bool row_sees_all = pos >= 0 && n0 >= vis_lo && n0 + B_BN <= kv_end && n0 + B_BN - 1 <= pos;
       if (!__all_sync(0xffffffffu, row_sees_all)) {
         const int rel = n0 - vis_lo;  // one unsigned compare per key: rel + i in [0, vis_span)
         const int rel_keep = n0 - kv_begin;
@@ -2167,7 +2198,7 @@ __global__ void __launch_bounds__(TC_THREADS, TC_STAGES == 2 ? 2 : 1) attn_tc_ke
         mx4[2] = fmaxf(mx4[2], s[i + 2]);
         mx4[3] = fmaxf(mx4[3], s[i + 3]);
       }
-      const float mx = fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3])) * a.scale_log2;  // the scale is positive
+      const float mx = fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3])) * sl2;  // the scale is positive
       m_true = fmaxf(m_true, mx);
       // The second product of the tile before is observed once per tile, always before this
       // thread allows the next one (the barrier's phases are then never two ahead of the
@@ -2210,7 +2241,7 @@ __global__ void __launch_bounds__(TC_THREADS, TC_STAGES == 2 ? 2 : 1) attn_tc_ke
 #pragma unroll
           for (int i = 0; i < 16; ++i) {
             float x0, x1;
-            fma_pair(x0, x1, s[half * 32 + 2 * i], s[half * 32 + 2 * i + 1], a.scale_log2, neg_m);
+            fma_pair(x0, x1, s[half * 32 + 2 * i], s[half * 32 + 2 * i + 1], sl2, neg_m);
             const float p0 = fast_exp2(x0), p1 = fast_exp2(x1);
             add_pair(sum4[2 * (i & 1)], sum4[2 * (i & 1) + 1], p0, p1);
             words[i] = pack_bf16(p0, p1);
@@ -2226,7 +2257,7 @@ __global__ void __launch_bounds__(TC_THREADS, TC_STAGES == 2 ? 2 : 1) attn_tc_ke
 #pragma unroll
           for (int i = 0; i < 8; i += 2) {
             float x0, x1;
-            fma_pair(x0, x1, s[c * 8 + i], s[c * 8 + i + 1], a.scale_log2, neg_m);
+            fma_pair(x0, x1, s[c * 8 + i], s[c * 8 + i + 1], sl2, neg_m);
             p[i] = fast_exp2(x0);
             p[i + 1] = fast_exp2(x1);
             add_pair(sum4[i & 2], sum4[(i & 2) + 1], p[i], p[i + 1]);
@@ -2423,8 +2454,6 @@ VX_API int vx_attention_scored(int kind, const void* q, void* out, const void* k
                                const float* bias_r1, const float* bias_r2, int chunk, int sink_zero,
                                const float* row_scale, int row_scale_len, cudaStream_t stream) {
   if (num_items <= 0) return 0;
-  const bool changed = softcap > 0.f || bias_r1 != nullptr || chunk > 0 || sink_zero != 0 || row_scale != nullptr;
-  if (changed && kind == 3) return (int)cudaErrorInvalidValue;
   if (sink_zero != 0 && (window > 0 || chunk > 0)) return (int)cudaErrorInvalidValue;
   // Only the narrow bf16 family shares an item among the CTAs of a cluster; for the
   // tensor-memory family 2 means "two CTAs on an SM" (see its launch below).

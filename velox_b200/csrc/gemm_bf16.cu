@@ -186,6 +186,16 @@ struct GemmArgs {
   // copy of the rows that stays as it is while a later kernel adds to `out` again.
   float* out2;
   long long ld2;
+  // Mode 3: with g = gate + bias[n] and u = up + bias[N + n] (bias [2 N] or null),
+  //   g <- min(g, glu_limit), u <- clamp(u, -glu_limit, glu_limit)   (glu_limit > 0)
+  //   out = g * sigmoid(glu_alpha * g) * (u + glu_shift)
+  // glu_alpha 1, glu_shift 0 and no limit: silu(gate) * up.
+  float glu_limit, glu_alpha, glu_shift;
+};
+
+// The gated activation of mode 3 with its options.
+struct GluArgs {
+  float limit, alpha, shift;
 };
 
 __device__ __forceinline__ void cluster_arrive() {
@@ -535,6 +545,8 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constan
         // rows 0..63 gate, 64..127 up of the same 64 output features
         const int n = n0 + (row & 63);
         __nv_bfloat16* out = (__nv_bfloat16*)g.out;
+        const bool biased = g.bias != nullptr && row < 64 && n < g.N;
+        const float bias_gate = biased ? g.bias[n] : 0.f, bias_up = biased ? g.bias[g.N + n] : 0.f;
         for (int c0 = 0; c0 < BN; c0 += 32) {
           float v[32];
           if (BN >= 32) tmem_load_32(lane_base + c0, v); else tmem_load_16(lane_base + c0, v);
@@ -548,8 +560,13 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constan
               const int t = t0 + c0 + j;
               if (t < g.T) {
                 const float scale = normed ? ssq_s[c0 + j] : 1.0f;
-                const float gate = v[j] * scale, up = swap_buf[row * 33 + j] * scale;
-                out[(size_t)t * g.ldy + n] = __float2bfloat16_rn(gate / (1.0f + __expf(-gate)) * up);
+                float gate = v[j] * scale + bias_gate, up = swap_buf[row * 33 + j] * scale + bias_up;
+                if (g.glu_limit > 0.f) {
+                  gate = fminf(gate, g.glu_limit);
+                  up = fminf(fmaxf(up, -g.glu_limit), g.glu_limit);
+                }
+                out[(size_t)t * g.ldy + n] =
+                    __float2bfloat16_rn(gate / (1.0f + __expf(-g.glu_alpha * gate)) * (up + g.glu_shift));
               }
             }
           }
@@ -557,7 +574,8 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constan
         }
       } else {
         const int n = n0 + row;
-        const float b = (g.bias != nullptr && n < g.N) ? g.bias[n] : 0.f;
+        // K in chunks of independent CTAs: the first chunk brings the bias.
+        const float b = (g.bias != nullptr && n < g.N && split == 0) ? g.bias[n] : 0.f;
         for (int c0 = 0; c0 < BN; c0 += 32) {
           float v[32];
           if (BN >= 32) tmem_load_32(lane_base + c0, v); else tmem_load_16(lane_base + c0, v);
@@ -1225,7 +1243,7 @@ static int gemm_bf16(const void* x, int x_rows, const float* resid, long long re
                      const float* norm_w, float eps, const void* w, const float* bias, void* out,
                      int mode, int T, int N, int K, long long ldy, int splits, int* status,
                      cudaStream_t stream, const RopeArgs* rope = nullptr, float* out2 = nullptr,
-                     long long ld2 = 0, int chunks = 1, const ActArgs* act = nullptr) {
+                     long long ld2 = 0, int chunks = 1, const ActArgs* act = nullptr, const GluArgs* glu = nullptr) {
   if (T <= 0 || N <= 0) return 0;
   if (K <= 0 || (K % 8) != 0) return -1;
   const bool normed = resid != nullptr;
@@ -1276,13 +1294,17 @@ static int gemm_bf16(const void* x, int x_rows, const float* resid, long long re
   g.act_from = act != nullptr ? act->act_from : 0;
   g.a_pos = act != nullptr ? act->a_pos : 0.f;
   g.a_neg = act != nullptr ? act->a_neg : 0.f;
+  if (glu != nullptr && mode != 3) return -1;
+  g.glu_limit = glu != nullptr && glu->limit > 0.f ? glu->limit : 0.f;
+  g.glu_alpha = glu != nullptr ? glu->alpha : 1.0f;
+  g.glu_shift = glu != nullptr ? glu->shift : 0.f;
   g.kb_per_split = (num_kb + splits - 1) / splits;
   g.splits = splits;
   // K in chunks of independent CTAs (mode 2 only): every CTA adds its partial tile to the output
   // by reductions at the L2, so no cluster and any number of chunks; the order of the additions
   // is then not fixed.
   if (chunks > 1) {
-    if (mode != 2 || normed || bias != nullptr || out2 != nullptr || rope != nullptr) return -1;
+    if (mode != 2 || normed || out2 != nullptr || rope != nullptr) return -1;
     if (chunks > num_kb) chunks = num_kb;
     g.splits = 1;
     g.kb_per_split = (num_kb + chunks - 1) / chunks;
@@ -1371,6 +1393,15 @@ VX_API int vx_gemm_bf16(const void* x, const void* w, const float* bias, void* o
                    status, stream);
 }
 
+// Mode 3 with the options of the gated activation (see GemmArgs): w [2 N, K] holds the N gate rows
+// and then the N up rows, bias [2 N] (or null) alike; out bf16 [T, ldy] has N columns.
+VX_API int vx_gemm_bf16_glu(const void* x, const void* w, const float* bias, void* out, int T, int x_rows, int N, int K,
+                            long long ldy, float limit, float alpha, float shift, int* status, cudaStream_t stream) {
+  const GluArgs glu = {limit, alpha, shift};
+  return gemm_bf16(x, x_rows, nullptr, 0, nullptr, 0.f, w, bias, out, 3, T, N, K, ldy, 1, status, stream, nullptr,
+                   nullptr, 0, 1, nullptr, &glu);
+}
+
 // Mode 5: out[t, n] = acc + bias for columns n < act_from (bf16, pitch ldy); the other columns go
 // through the xIELU activation into act_out [T, act_ld] at column n - act_from.  One launch makes a
 // feed-forward's inner activations and the columns that ride along with its first projection.
@@ -1398,9 +1429,10 @@ VX_API int vx_gemm_bf16_add_mirrored(const void* x, const void* w, float* out, f
 // each adds its partial tile to `out` by float32 reductions at the L2.  Fills the GPU whatever
 // the number of output tiles (a cluster holds eight CTAs at most and wants a power of two);
 // the order of the additions, and with it the last bits of the sums, is not fixed.
-VX_API int vx_gemm_bf16_add_chunked(const void* x, const void* w, float* out, int T, int x_rows, int N, int K,
-                                    long long ldy, int chunks, int* status, cudaStream_t stream) {
-  return gemm_bf16(x, x_rows, nullptr, 0, nullptr, 0.f, w, nullptr, out, 2, T, N, K, ldy, 1, status, stream,
+// A bias [N] (or null) is added once, by the CTAs of the first range.
+VX_API int vx_gemm_bf16_add_chunked(const void* x, const void* w, const float* bias, float* out, int T, int x_rows,
+                                    int N, int K, long long ldy, int chunks, int* status, cudaStream_t stream) {
+  return gemm_bf16(x, x_rows, nullptr, 0, nullptr, 0.f, w, bias, out, 2, T, N, K, ldy, 1, status, stream,
                    nullptr, nullptr, 0, chunks < 1 ? 1 : chunks);
 }
 

@@ -23,6 +23,37 @@ namespace vx {
 
 __device__ __forceinline__ float hd_sigmoid(float v) { return 1.0f / (1.0f + expf(-v)); }
 
+// Sixteen bytes of a row at a time: four float32 or eight bfloat16, as floats.
+template <typename T>
+struct Pack {
+  static constexpr int N = 16 / (int)sizeof(T);
+};
+__device__ __forceinline__ void load_pack(const float* p, float (&v)[4]) {
+  const float4 x = *reinterpret_cast<const float4*>(p);
+  v[0] = x.x, v[1] = x.y, v[2] = x.z, v[3] = x.w;
+}
+__device__ __forceinline__ void load_pack(const __nv_bfloat16* p, float (&v)[8]) {
+  const uint4 x = *reinterpret_cast<const uint4*>(p);
+  const uint32_t w[4] = {x.x, x.y, x.z, x.w};
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    v[2 * i] = __uint_as_float(w[i] << 16);
+    v[2 * i + 1] = __uint_as_float(w[i] & 0xffff0000u);
+  }
+}
+__device__ __forceinline__ void store_pack(float* p, const float (&v)[4]) {
+  *reinterpret_cast<float4*>(p) = make_float4(v[0], v[1], v[2], v[3]);
+}
+__device__ __forceinline__ void store_pack(__nv_bfloat16* p, const float (&v)[8]) {
+  uint32_t w[4];
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    const __nv_bfloat162 h = __floats2bfloat162_rn(v[2 * i], v[2 * i + 1]);
+    w[i] = *reinterpret_cast<const uint32_t*>(&h);
+  }
+  *reinterpret_cast<uint4*>(p) = make_uint4(w[0], w[1], w[2], w[3]);
+}
+
 // ---------------------------------------------------------------------------------------------
 // Token shift.  With h_t = x_t / rms(x_t) * w1 the first output of row t is
 //     h_t + (h_(t-1) - h_t) * shift
@@ -93,6 +124,129 @@ __global__ void norm_shift_kernel(const float* __restrict__ resid, long long res
   }
 }
 
+// Two sums over a block at once; every thread gets both.
+__device__ __forceinline__ void block_sum2(float& a, float& b, float* scratch /* >= 64 floats */) {
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const int num_warps = (blockDim.x + 31) >> 5;
+  a = warp_sum(a);
+  b = warp_sum(b);
+  if (lane == 0) {
+    scratch[warp] = a;
+    scratch[32 + warp] = b;
+  }
+  __syncthreads();
+  a = warp_sum(lane < num_warps ? scratch[lane] : 0.f);
+  b = warp_sum(lane < num_warps ? scratch[32 + lane] : 0.f);
+  __syncthreads();
+}
+
+__device__ __forceinline__ float sum_squares4(const float* p) {
+  const float4 v = *reinterpret_cast<const float4*>(p);
+  return v.x * v.x + v.y * v.y + v.z * v.z + v.w * v.w;
+}
+
+// The same with sixteen bytes per access (width a multiple of the outputs' pack, every row
+// 16-byte aligned): the statistics of the row and of the row before it in one pass; a portion of
+// one token (decode) writes the h it has just made into the state row instead of norming the
+// row a second time.
+template <typename T>
+__global__ void norm_shift_vec_kernel(const float* __restrict__ resid, long long resid_stride, int width, float eps,
+                                      const float* __restrict__ w1, const float* __restrict__ w2,
+                                      const float* __restrict__ shift, float* __restrict__ state,
+                                      long long state_stride, T* __restrict__ out1, T* __restrict__ out2,
+                                      const int* __restrict__ q_start, const int* __restrict__ q_len,
+                                      const int* __restrict__ seq_slots, int num_seqs) {
+  constexpr int N = Pack<T>::N;
+  __shared__ float scratch[64];
+  allow_dependents();
+  const int t = blockIdx.x;
+  int seq = -1, first = 0, last = 0;
+  for (int s0 = 0; s0 < num_seqs; s0 += 32) {
+    const int s = s0 + (threadIdx.x & 31);
+    const int b = s < num_seqs ? q_start[s] : 0, n = s < num_seqs ? q_len[s] : 0;
+    const unsigned hit = __ballot_sync(0xffffffffu, n > 0 && t >= b && t < b + n);
+    if (hit != 0u) {
+      const int src = 31 - __clz(hit);  // the last one that claims the row, as the loop form has it
+      seq = s0 + src;
+      first = __shfl_sync(0xffffffffu, b, src);
+      last = first + __shfl_sync(0xffffffffu, n, src) - 1;
+    }
+  }
+  grid_dependency_wait();
+  const float* x = resid + (size_t)t * resid_stride;
+  const bool shifted = shift != nullptr;
+  const bool in_seq = shifted && seq >= 0;
+  const float* prev_x = in_seq && t > first ? x - resid_stride : nullptr;
+  float* own_state = in_seq && t == first ? state + (size_t)seq_slots[seq] * state_stride : nullptr;
+  float ss = 0.f, ps = 0.f;
+  for (int i = threadIdx.x * 4; i < width; i += blockDim.x * 4) {
+    ss += sum_squares4(x + i);
+    if (prev_x != nullptr) ps += sum_squares4(prev_x + i);
+  }
+  block_sum2(ss, ps, scratch);
+  const float r = rsqrtf(ss / (float)width + eps), prev_r = rsqrtf(ps / (float)width + eps);
+  const bool state_now = own_state != nullptr && first == last;
+  for (int i = threadIdx.x * N; i < width; i += blockDim.x * N) {
+    float h[N], n[N], o[N];
+#pragma unroll
+    for (int j = 0; j < N; j += 4) {
+      float xv[4], wv[4];
+      load_pack(x + i + j, xv);
+      load_pack(w1 + i + j, wv);
+#pragma unroll
+      for (int e = 0; e < 4; ++e) {
+        n[j + e] = xv[e] * r;
+        h[j + e] = n[j + e] * wv[e];
+        o[j + e] = h[j + e];
+      }
+      if (shifted) {
+        float before[4] = {0.f, 0.f, 0.f, 0.f}, sv[4];
+        if (prev_x != nullptr) {
+          load_pack(prev_x + i + j, before);
+#pragma unroll
+          for (int e = 0; e < 4; ++e) before[e] = before[e] * prev_r * wv[e];
+        } else if (own_state != nullptr) {
+          load_pack(own_state + i + j, before);
+        }
+        load_pack(shift + i + j, sv);
+#pragma unroll
+        for (int e = 0; e < 4; ++e) o[j + e] = h[j + e] + (before[e] - h[j + e]) * sv[e];
+      }
+      if (state_now) {
+        const float hv[4] = {h[j], h[j + 1], h[j + 2], h[j + 3]};
+        store_pack(own_state + i + j, hv);  // read just above by this thread, by nobody else
+      }
+    }
+    store_pack(out1 + (size_t)t * width + i, o);
+    if (w2 != nullptr) {
+#pragma unroll
+      for (int j = 0; j < N; j += 4) {
+        float wv[4];
+        load_pack(w2 + i + j, wv);
+#pragma unroll
+        for (int e = 0; e < 4; ++e) o[j + e] = n[j + e] * wv[e];
+      }
+      store_pack(out2 + (size_t)t * width + i, o);
+    }
+  }
+  if (own_state != nullptr && first != last) {
+    __syncthreads();
+    const float* xl = resid + (size_t)last * resid_stride;
+    float ls = 0.f, unused = 0.f;
+    for (int i = threadIdx.x * 4; i < width; i += blockDim.x * 4) ls += sum_squares4(xl + i);
+    block_sum2(ls, unused, scratch);
+    const float lr = rsqrtf(ls / (float)width + eps);
+    for (int i = threadIdx.x * 4; i < width; i += blockDim.x * 4) {
+      float xv[4], wv[4];
+      load_pack(xl + i, xv);
+      load_pack(w1 + i, wv);
+#pragma unroll
+      for (int e = 0; e < 4; ++e) xv[e] = xv[e] * lr * wv[e];
+      store_pack(own_state + i, xv);
+    }
+  }
+}
+
 template <typename T>
 __global__ void add_rows_kernel(float* __restrict__ resid, const T* __restrict__ a, const T* __restrict__ b,
                                 long long count) {
@@ -103,6 +257,33 @@ __global__ void add_rows_kernel(float* __restrict__ resid, const T* __restrict__
     float v = resid[i] + to_float(a[i]);
     if (b != nullptr) v += to_float(b[i]);
     resid[i] = v;
+  }
+}
+
+template <typename T>
+__global__ void add_rows_vec_kernel(float* __restrict__ resid, const T* __restrict__ a, const T* __restrict__ b,
+                                    long long packs) {
+  constexpr int N = Pack<T>::N;
+  allow_dependents();
+  grid_dependency_wait();
+  for (long long p = (long long)blockIdx.x * blockDim.x + threadIdx.x; p < packs;
+       p += (long long)gridDim.x * blockDim.x) {
+    const long long i = p * N;
+    float av[N], bv[N];
+    load_pack(a + i, av);
+    if (b != nullptr) {
+      load_pack(b + i, bv);
+#pragma unroll
+      for (int e = 0; e < N; ++e) av[e] += bv[e];
+    }
+#pragma unroll
+    for (int j = 0; j < N; j += 4) {
+      float xv[4];
+      load_pack(resid + i + j, xv);
+#pragma unroll
+      for (int e = 0; e < 4; ++e) xv[e] += av[j + e];
+      store_pack(resid + i + j, xv);
+    }
   }
 }
 
@@ -212,6 +393,49 @@ __global__ void diff_combine_kernel(const T* __restrict__ attn, long long attn_s
   }
 }
 
+// The same with sixteen bytes per access (vdim, D and the pitches multiples of the pack).
+template <typename T>
+__global__ void diff_combine_vec_kernel(const T* __restrict__ attn, long long attn_stride, const T* __restrict__ gate,
+                                        long long gate_stride, T* __restrict__ out, long long out_stride, int H,
+                                        int vdim, int D, float lambda, float out_scale, float eps) {
+  constexpr int N = Pack<T>::N;
+  allow_dependents();
+  grid_dependency_wait();
+  const int t = blockIdx.x;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int h = blockIdx.y * (blockDim.x >> 5) + warp;
+  if (h >= H) return;
+  const T* a1 = attn + (size_t)t * attn_stride + (size_t)(2 * h) * D;
+  const T* a2 = a1 + D;
+  float ss = 0.f;
+  for (int i = lane * N; i < vdim; i += 32 * N) {
+    float x[N], y[N];
+    load_pack(a1 + i, x);
+    load_pack(a2 + i, y);
+#pragma unroll
+    for (int e = 0; e < N; ++e) {
+      const float o = x[e] - lambda * y[e];
+      ss += o * o;
+    }
+  }
+  const float r = rsqrtf(warp_sum(ss) / (float)vdim + eps) * out_scale;
+  const T* g = gate != nullptr ? gate + (size_t)t * gate_stride + (size_t)h * vdim : nullptr;
+  T* dst = out + (size_t)t * out_stride + (size_t)h * vdim;
+  for (int i = lane * N; i < vdim; i += 32 * N) {
+    float x[N], y[N];
+    load_pack(a1 + i, x);
+    load_pack(a2 + i, y);
+#pragma unroll
+    for (int e = 0; e < N; ++e) x[e] = (x[e] - lambda * y[e]) * r;
+    if (g != nullptr) {
+      load_pack(g + i, y);
+#pragma unroll
+      for (int e = 0; e < N; ++e) x[e] *= hd_sigmoid(y[e]);
+    }
+    store_pack(dst + i, x);
+  }
+}
+
 // gate_up [tokens][2 F] (gate columns first) -> out [tokens][F].
 template <typename T>
 __global__ void clamped_glu_kernel(const T* __restrict__ gate_up, long long in_stride, T* __restrict__ out,
@@ -233,6 +457,32 @@ __global__ void clamped_glu_kernel(const T* __restrict__ gate_up, long long in_s
   }
 }
 
+// The same, sixteen bytes of gate and of up per thread (F and both pitches multiples of the pack).
+template <typename T>
+__global__ void clamped_glu_vec_kernel(const T* __restrict__ gate_up, long long in_stride, T* __restrict__ out,
+                                       long long out_stride, int F, float limit, float alpha, float up_shift) {
+  constexpr int N = Pack<T>::N;
+  allow_dependents();
+  grid_dependency_wait();
+  const T* row = gate_up + (size_t)blockIdx.y * in_stride;
+  T* dst = out + (size_t)blockIdx.y * out_stride;
+  for (int f = (blockIdx.x * blockDim.x + threadIdx.x) * N; f < F; f += gridDim.x * blockDim.x * N) {
+    float g[N], u[N];
+    load_pack(row + f, g);
+    load_pack(row + F + f, u);
+#pragma unroll
+    for (int e = 0; e < N; ++e) {
+      float gv = g[e], uv = u[e];
+      if (limit > 0.f) {
+        gv = fminf(gv, limit);
+        uv = fminf(fmaxf(uv, -limit), limit);
+      }
+      g[e] = gv * hd_sigmoid(alpha * gv) * (uv + up_shift);
+    }
+    store_pack(dst + f, g);
+  }
+}
+
 }  // namespace vx
 
 using namespace vx;
@@ -248,6 +498,8 @@ using namespace vx;
     return (int)cudaErrorInvalidValue;            \
   }
 
+static bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15) == 0; }
+
 static int row_threads(int width) {
   const int t = (width + 31) / 32 * 32;
   return t > 512 ? 512 : (t < 32 ? 32 : t);
@@ -259,6 +511,15 @@ VX_API int vx_norm_shift(const float* resid, long long resid_stride, int width, 
                          int num_seqs, int num_tokens, cudaStream_t stream) {
   if (num_tokens <= 0) return 0;
   if (shift != nullptr && state == nullptr) return (int)cudaErrorInvalidValue;
+  const int pack = dtype == VX_DTYPE_F32 ? 4 : 8;
+  const bool vec = width % pack == 0 && resid_stride % 4 == 0 && aligned16(resid) && aligned16(w1) && aligned16(w2) &&
+                   aligned16(shift) && aligned16(state) && state_stride % 4 == 0 && aligned16(out1) && aligned16(out2);
+  if (vec) {
+    VX_BY_DTYPE(dtype, launch_pdl(norm_shift_vec_kernel<T>, dim3(num_tokens), dim3(row_threads(width / pack)), 0, stream,
+                                  resid, resid_stride, width, eps, w1, w2, shift, state, state_stride, (T*)out1,
+                                  (T*)out2, q_start, q_len, seq_slots, num_seqs));
+    return (int)cudaGetLastError();
+  }
   VX_BY_DTYPE(dtype, launch_pdl(norm_shift_kernel<T>, dim3(num_tokens), dim3(row_threads(width)), 0, stream, resid,
                                 resid_stride, width, eps, w1, w2, shift, state, state_stride, (T*)out1, (T*)out2,
                                 q_start, q_len, seq_slots, num_seqs));
@@ -267,6 +528,15 @@ VX_API int vx_norm_shift(const float* resid, long long resid_stride, int width, 
 
 VX_API int vx_add_rows(float* resid, const void* a, const void* b, int dtype, long long count, cudaStream_t stream) {
   if (count <= 0) return 0;
+  const int pack = dtype == VX_DTYPE_F32 ? 4 : 8;
+  if (count % pack == 0 && aligned16(resid) && aligned16(a) && aligned16(b)) {
+    const long long packs = count / pack;
+    long long vec_blocks = (packs + 255) / 256;
+    if (vec_blocks > 148 * 8) vec_blocks = 148 * 8;
+    VX_BY_DTYPE(dtype, launch_pdl(add_rows_vec_kernel<T>, dim3((unsigned)vec_blocks), dim3(256), 0, stream, resid,
+                                  (const T*)a, (const T*)b, packs));
+    return (int)cudaGetLastError();
+  }
   long long blocks = (count + 255) / 256;
   if (blocks > 148 * 16) blocks = 148 * 16;
   VX_BY_DTYPE(dtype, launch_pdl(add_rows_kernel<T>, dim3((unsigned)blocks), dim3(256), 0, stream, resid,
@@ -294,6 +564,14 @@ VX_API int vx_diff_combine(const void* attn, int dtype, long long attn_stride, c
                            int D, float lambda, float out_scale, float eps, cudaStream_t stream) {
   if (num_tokens <= 0) return 0;
   const dim3 grid(num_tokens, (H + 3) / 4);
+  const int pack = dtype == VX_DTYPE_F32 ? 4 : 8;
+  if (vdim % pack == 0 && D % pack == 0 && attn_stride % pack == 0 && gate_stride % pack == 0 &&
+      out_stride % pack == 0 && aligned16(attn) && aligned16(gate) && aligned16(out)) {
+    VX_BY_DTYPE(dtype, launch_pdl(diff_combine_vec_kernel<T>, grid, dim3(128), 0, stream, (const T*)attn, attn_stride,
+                                  (const T*)gate, gate_stride, (T*)out, out_stride, H, vdim, D, lambda, out_scale,
+                                  eps));
+    return (int)cudaGetLastError();
+  }
   VX_BY_DTYPE(dtype, launch_pdl(diff_combine_kernel<T>, grid, dim3(128), 0, stream, (const T*)attn, attn_stride,
                                 (const T*)gate, gate_stride, (T*)out, out_stride, H, vdim, D, lambda, out_scale,
                                 eps));
@@ -303,6 +581,16 @@ VX_API int vx_diff_combine(const void* attn, int dtype, long long attn_stride, c
 VX_API int vx_clamped_glu(const void* gate_up, int dtype, long long in_stride, void* out, long long out_stride,
                           int num_tokens, int F, float limit, float alpha, float up_shift, cudaStream_t stream) {
   if (num_tokens <= 0 || F <= 0) return 0;
+  const int pack = dtype == VX_DTYPE_F32 ? 4 : 8;
+  if (F % pack == 0 && in_stride % pack == 0 && out_stride % pack == 0 && aligned16(gate_up) && aligned16(out) &&
+      num_tokens <= 65535) {
+    const int threads = 128;
+    int across = (F / pack + threads - 1) / threads;
+    if (across > 32) across = 32;
+    VX_BY_DTYPE(dtype, launch_pdl(clamped_glu_vec_kernel<T>, dim3(across, num_tokens), dim3(threads), 0, stream,
+                                  (const T*)gate_up, in_stride, (T*)out, out_stride, F, limit, alpha, up_shift));
+    return (int)cudaGetLastError();
+  }
   const long long count = (long long)num_tokens * F;
   long long blocks = (count + 255) / 256;
   if (blocks > 148 * 16) blocks = 148 * 16;

@@ -73,12 +73,15 @@ def core():
         lib.vx_gemm_bf16.argtypes = [
             _ptr, _ptr, _ptr, _ptr, _c_int, _c_int, _c_int, _c_int, _c_int, _c_ll, _c_int, _ptr, _ptr,
         ]
+        lib.vx_gemm_bf16_glu.argtypes = [
+            _ptr, _ptr, _ptr, _ptr, _c_int, _c_int, _c_int, _c_int, _c_ll, _c_f, _c_f, _c_f, _ptr, _ptr,
+        ]
         lib.vx_gemm_bf16_xielu.argtypes = [
             _ptr, _ptr, _ptr, _ptr, _ptr, _c_int, _c_int, _c_int, _c_int, _c_ll, _c_ll, _c_int, _c_f, _c_f, _c_int,
             _ptr, _ptr,
         ]
         lib.vx_gemm_bf16_add_chunked.argtypes = [
-            _ptr, _ptr, _ptr, _c_int, _c_int, _c_int, _c_int, _c_ll, _c_int, _ptr, _ptr,
+            _ptr, _ptr, _ptr, _ptr, _c_int, _c_int, _c_int, _c_int, _c_ll, _c_int, _ptr, _ptr,
         ]
         lib.vx_gemm_bf16_normed.argtypes = [
             _ptr, _c_ll, _ptr, _c_f, _ptr, _ptr, _ptr, _c_int, _c_int, _c_int, _c_int, _c_ll, _c_int, _ptr, _ptr,
@@ -732,6 +735,29 @@ def gemm_bf16(
     _check(code, "gemm_bf16")
 
 
+def gemm_bf16_glu(x: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor], out: torch.Tensor, num_rows: int,
+                  limit: float, alpha: float, up_shift: float, status: torch.Tensor) -> None:
+    """out[:num_rows] = g * sigmoid(alpha * g) * (u + up_shift) with g and u the two halves of
+    x[:num_rows] @ w.T + bias (w [2 F, K]: the F gate rows, then the F up rows; bias [2 F] float32
+    or None), g cut at ``limit`` from above and u to +-``limit`` when ``limit`` > 0, in the
+    epilogue of the tcgen05 kernel: the activations' inputs never leave the SM."""
+    _need(x, torch.bfloat16, "x")
+    _need(w, torch.bfloat16, "w")
+    _need(out, torch.bfloat16, "out")
+    n, k = w.shape
+    if n % 2 or x.shape[1] != k or out.dim() != 2 or out.shape[1] != n // 2:
+        raise ValueError(f"gemm shapes do not agree: x {tuple(x.shape)}, w {tuple(w.shape)}, out {tuple(out.shape)}")
+    if bias is not None:
+        _need(bias, torch.float32, "bias")
+        if bias.numel() != n:
+            raise ValueError(f"bias of {bias.numel()} elements for {n} rows")
+    code = core().vx_gemm_bf16_glu(_p(x), _p(w), _p(bias), _p(out), num_rows, x.shape[0], n // 2, k, out.stride(0),
+                                   float(limit), float(alpha), float(up_shift), _p(status), _stream())
+    if code == -1:
+        raise KernelError(f"gemm_bf16_glu refuses x {tuple(x.shape)} w {tuple(w.shape)}")
+    _check(code, "gemm_bf16_glu")
+
+
 def gemm_bf16_xielu(
     x: torch.Tensor,
     w: torch.Tensor,
@@ -770,8 +796,8 @@ def gemm_bf16_xielu(
 
 
 def gemm_bf16_add_chunked(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, num_rows: int,
-                          status: torch.Tensor, chunks: int) -> None:
-    """out[:num_rows] += x[:num_rows] @ w.T (float32 ``out``) with the inner dimension cut into
+                          status: torch.Tensor, chunks: int, bias: Optional[torch.Tensor] = None) -> None:
+    """out[:num_rows] += x[:num_rows] @ w.T (+ bias) (float32 ``out``) with the inner dimension cut into
     ``chunks`` ranges taken by independent CTAs, which add their partial tiles to ``out`` by
     reductions at the L2: any number of CTAs per output tile, no cluster, and an order of
     additions that is not fixed."""
@@ -781,7 +807,11 @@ def gemm_bf16_add_chunked(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, n
     n, k = w.shape
     if x.shape[1] != k or out.dim() != 2 or out.shape[1] != n:
         raise ValueError(f"gemm shapes do not agree: x {tuple(x.shape)}, w {tuple(w.shape)}, out {tuple(out.shape)}")
-    code = core().vx_gemm_bf16_add_chunked(_p(x), _p(w), _p(out), num_rows, x.shape[0], n, k, out.stride(0),
+    if bias is not None:
+        _need(bias, torch.float32, "bias")
+        if bias.numel() != n:
+            raise ValueError(f"bias of {bias.numel()} elements for {n} outputs")
+    code = core().vx_gemm_bf16_add_chunked(_p(x), _p(w), _p(bias), _p(out), num_rows, x.shape[0], n, k, out.stride(0),
                                            int(chunks), _p(status), _stream())
     if code == -1:
         raise KernelError(f"gemm_bf16_add_chunked refuses x {tuple(x.shape)} w {tuple(w.shape)}")

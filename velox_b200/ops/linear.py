@@ -142,8 +142,8 @@ def linear(
             return out
         if accumulate:
             chunks = choose_chunks(weight.shape[0], weight.shape[1], num_rows) if _CHUNKED_SPLITK else 1
-            if chunks > 1 and bias_f32 is None:
-                kernels.gemm_bf16_add_chunked(x, weight, out, num_rows, status, chunks)
+            if chunks > 1:
+                kernels.gemm_bf16_add_chunked(x, weight, out, num_rows, status, chunks, bias=bias_f32)
                 return out
             mode = kernels.GEMM_ADD_F32
         else:

@@ -19,8 +19,8 @@ Changes to the scores, made inside the attention kernels: ``distance_bias`` (wei
 ``bias_r2``, one number each per query head): ``r1 ln(1 + r2 (i - j))`` is taken off the score of
 query i and key j; ``sink_zero``: one more term of score 0 and no value in every softmax
 denominator (without a window); a position part with a ``row_scale`` table (``log_temperature``)
-multiplies a query's scores by a number that depends on its position.  Layers with any of these
-run on the float32, wide and narrow kernel families.
+multiplies a query's scores by a number that depends on its position.  Every kernel family takes
+them.
 """
 from __future__ import annotations
 
@@ -145,9 +145,6 @@ class Attention(Mixer):
 
     def attention_signature(self):
         base = (self.num_kv_heads, self.num_heads // self.num_kv_heads, self.window, self.head_dim)
-        if self.scored:
-            # Changed scores: no tensor-memory family in the layout.
-            return base + (self.keep_first, self.anchored, (("wide_on_tensor_memory", False),))
         return base + (self.keep_first, True) if self.anchored else base
 
     # The input is used by the QKV projection only, which can make the norm itself.

@@ -229,10 +229,16 @@ class ParallelBlock:
         if self.feed_forward is None:
             hidden.delta = mixed
         else:
-            if mixed is not None:
-                if self.shift is None and not self.two_outputs:
+            if self.shift is None and not self.two_outputs:
+                if mixed is not None:
                     kernels.residual_add(hidden.resid, mixed, T)
+                hidden.delta = self.feed_forward.forward(for_feed_forward, ctx)
+            else:
+                # Both products were made from the same rows, so they go into the stream together,
+                # in one pass over it; nothing stays pending for the next block's norms.
+                product = self.feed_forward.forward(for_feed_forward, ctx)
+                if mixed is not None:
+                    kernels.add_rows(hidden.resid, mixed, product, T)
                 else:
-                    kernels.add_rows(hidden.resid, mixed, None, T)
-            hidden.delta = self.feed_forward.forward(for_feed_forward, ctx)
+                    hidden.delta = product
         ctx.residual = None

@@ -91,7 +91,7 @@ class DifferentialAttention(Mixer):
         return CacheNeeds(paged=PagedCacheSpec(self.num_kv_heads, self.head_dim, None, chunk=self.chunk))
 
     def attention_signature(self):
-        options = (("chunk", self.chunk), ("wide_on_tensor_memory", False))
+        options = (("chunk", self.chunk),)
         return (self.num_kv_heads, 2 * self.num_heads // self.num_kv_heads, None, self.head_dim, 0, False, options)
 
     def forward(self, x, ctx, cache):

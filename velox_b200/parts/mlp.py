@@ -251,10 +251,15 @@ class ClampedGLU(FeedForward):
         if hasattr(x, "materialize"):
             x = x.materialize()
         Fp = self.inner
-        gate_up = ws.get(f"clamped_glu.gate_up{2 * Fp}", (ws.max_tokens, 2 * Fp), self.dtype)
-        linear(x, self.w_gate_up, self.b_gate_up, gate_up, T, self.b_gate_up_lowp, status=ctx.status)
         act = ws.get(f"clamped_glu.act{Fp}", (ws.max_tokens, Fp), self.dtype)
-        kernels.clamped_glu(gate_up, act, T, Fp, self.limit, self.alpha, self.up_shift)
+        if ctx.status is not None and use_tensor_core_kernel(x, self.w_gate_up, T):
+            # Few tokens: biases, clamps and activation in the projection's epilogue.
+            kernels.gemm_bf16_glu(x, self.w_gate_up, self.b_gate_up, act, T, self.limit, self.alpha, self.up_shift,
+                                  ctx.status)
+        else:
+            gate_up = ws.get(f"clamped_glu.gate_up{2 * Fp}", (ws.max_tokens, 2 * Fp), self.dtype)
+            linear(x, self.w_gate_up, self.b_gate_up, gate_up, T, self.b_gate_up_lowp, status=ctx.status)
+            kernels.clamped_glu(gate_up, act, T, Fp, self.limit, self.alpha, self.up_shift)
         if (ctx.residual is not None and ctx.status is not None and self.dtype != torch.float32
                 and use_tensor_core_kernel(act, self.w_down, T)):
             # Few tokens: the down projection (and its bias) goes straight into the float32 stream.
