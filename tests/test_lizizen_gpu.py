@@ -219,7 +219,8 @@ MIXED = [(70, 0), (1, 0), (1, 130), (2, 61), (33, 100), (1, 63), (1, 64), (17, 1
 
 
 @pytest.mark.parametrize("dtype", list(DTYPES))
-@pytest.mark.parametrize("H,G,D,P", [(4, 2, 16, 4), (5, 5, 48, 16), (6, 2, 80, 16), (12, 2, 128, 16), (32, 1, 64, 16)])
+@pytest.mark.parametrize("H,G,D,P", [(4, 2, 16, 4), (5, 5, 48, 16), (6, 2, 80, 16), (12, 2, 128, 16), (32, 1, 64, 16),
+                                     (3, 1, 112, 16), (2, 2, 192, 8)])
 def test_attention_with_bias_temperature_and_zero_sink(dtype, H, G, D, P):
     """Whole prompts, portions with context, single decoded tokens, a first token and a portion
     of two tokens: distance bias, a factor per query position and the term of score 0."""
@@ -287,7 +288,8 @@ def test_changed_scores_on_the_tensor_memory_family(H, G, D, P, change):
 
 @pytest.mark.parametrize("dtype", list(DTYPES))
 @pytest.mark.parametrize("H,G,dim,vdim,D,rot", [(4, 2, 16, 24, 32, 8), (3, 3, 12, 20, 32, 12), (1, 1, 20, 12, 48, 0),
-                                                (4, 1, 128, 96, 256, 64), (6, 2, 10, 6, 32, 4)])
+                                                (4, 1, 128, 96, 256, 64), (6, 2, 10, 6, 32, 4), (6, 2, 64, 128, 128, 32),
+                                                (2, 1, 32, 64, 64, 0), (5, 1, 16, 8, 32, 16)])
 @pytest.mark.parametrize("pad", [5, 0])
 def test_differential_attention_ends(dtype, H, G, dim, vdim, D, rot, pad):
     """Before the attention kernels: norm and rotation per head and map, the maps' places in a

@@ -371,6 +371,126 @@ __global__ void diff_prepare_kernel(const T* __restrict__ proj, long long stride
   }
 }
 
+// The same with sixteen bytes per access: a unit belongs to a group of `gl` lanes (a power of two,
+// at least dim / pack), so a warp takes 32 / gl units; a lane holds one pack of its unit and, in
+// the rotated dims, the pack of the partner dims; every load is asked for before the group's sum.
+// Wants dim, rot / 2, vdim, D and the pitches as multiples of the pack and 16-byte aligned rows.
+template <typename T>
+__global__ void diff_prepare_vec_kernel(const T* __restrict__ proj, long long stride, T* __restrict__ qbuf,
+                                        long long q_stride, const int* __restrict__ positions,
+                                        const float* __restrict__ cos_t, const float* __restrict__ sin_t,
+                                        const float* __restrict__ q_norm, const float* __restrict__ k_norm,
+                                        float eps, const int* __restrict__ slots, T* __restrict__ k_cache,
+                                        T* __restrict__ v_cache, int H, int G, int dim, int vdim, int D, int rot,
+                                        int max_pos, long long num_slots, int write_cache, int* status, int gl) {
+  constexpr int N = Pack<T>::N;
+  allow_dependents();
+  grid_dependency_wait();
+  const int t = blockIdx.x;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int unit = (blockIdx.y * (blockDim.x >> 5) + warp) * (32 / gl) + lane / gl;
+  const int gi = lane % gl;
+  const int q_units = 2 * H, k_units = 2 * G;
+  const T* row = proj + (size_t)t * stride;
+  bool active = unit < q_units + k_units + G;
+  int slot = -1;
+  if (active && unit >= q_units) {
+    slot = write_cache ? slots[t] : -1;
+    if (slot >= 0 && (long long)slot >= num_slots) {
+      if (gi == 0) atomicOr(status, VX_STATUS_BAD_SLOT);
+      slot = -1;
+    }
+    active = slot >= 0;
+  }
+  if (active && unit >= q_units + k_units) {
+    const int g = unit - q_units - k_units;
+    const T* src = row + (size_t)(q_units + k_units) * dim + (size_t)g * vdim;
+    T* dst = v_cache + ((size_t)slot * G + g) * D;
+    for (int i = gi * N; i < vdim; i += gl * N) {
+      float v[N];
+      load_pack(src + i, v);
+      store_pack(dst + i, v);
+    }
+    active = false;
+  }
+  // q and k units; lanes of other units keep zeros and take part in the shuffles only.
+  const bool is_q = unit < q_units;
+  const int u = is_q ? unit : unit - q_units;
+  const int map = u & 1;
+  const int i = gi * N;
+  const bool on = active && i < dim;
+  const bool turned = on && i < rot;
+  const int half = rot >> 1;
+  const int partner = i < half ? i + half : i - half;
+  const T* src = row + (size_t)unit * dim;
+  const float* w = is_q ? q_norm : k_norm;
+  int pos = 0;
+  if (turned) {
+    pos = positions[t];
+    if (pos < 0 || pos >= max_pos) {
+      if (gi == 0 && unit == 0) atomicOr(status, VX_STATUS_BAD_POSITION);
+      pos = 0;
+    }
+  }
+  float x[N], o[N], wx[N], wo[N], c[N], sn[N];
+#pragma unroll
+  for (int e = 0; e < N; ++e) {
+    x[e] = o[e] = c[e] = sn[e] = 0.f;
+    wx[e] = wo[e] = 1.0f;
+  }
+  if (on) {
+    load_pack(src + i, x);
+    if (w != nullptr) {
+#pragma unroll
+      for (int j = 0; j < N; j += 4) {
+        float part[4];
+        load_pack(w + i + j, part);
+#pragma unroll
+        for (int e = 0; e < 4; ++e) wx[j + e] = part[e];
+      }
+    }
+  }
+  if (turned) {
+    load_pack(src + partner, o);
+    const int j0 = i < half ? i : i - half;
+#pragma unroll
+    for (int j = 0; j < N; j += 4) {
+      float part[4];
+      if (w != nullptr) {
+        load_pack(w + partner + j, part);
+#pragma unroll
+        for (int e = 0; e < 4; ++e) wo[j + e] = part[e];
+      }
+      load_pack(cos_t + (size_t)pos * half + j0 + j, part);
+#pragma unroll
+      for (int e = 0; e < 4; ++e) c[j + e] = part[e];
+      load_pack(sin_t + (size_t)pos * half + j0 + j, part);
+#pragma unroll
+      for (int e = 0; e < 4; ++e) sn[j + e] = part[e];
+    }
+  }
+  float ss = 0.f;
+#pragma unroll
+  for (int e = 0; e < N; ++e) ss += x[e] * x[e];
+  for (int offset = gl >> 1; offset > 0; offset >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, offset);
+  if (!on) return;
+  const float r = w != nullptr ? rsqrtf(ss / (float)dim + eps) : 1.0f;
+#pragma unroll
+  for (int e = 0; e < N; ++e) {
+    const float v = x[e] * r * wx[e];
+    if (turned) {
+      const float other = o[e] * r * wo[e];
+      // (u, v) -> (u cos - v sin, v cos + u sin) for the pair (j, j + half)
+      x[e] = i < half ? v * c[e] - other * sn[e] : v * c[e] + other * sn[e];
+    } else {
+      x[e] = v;
+    }
+  }
+  T* dst = is_q ? qbuf + (size_t)t * q_stride + (size_t)unit * D + (size_t)map * dim
+                : k_cache + ((size_t)slot * G + (u >> 1)) * D + (size_t)map * dim;
+  store_pack(dst + i, x);
+}
+
 // After the attention kernels: attn[t][2 h + m][0 .. vdim) is map m of head h.  A warp per
 // (token, head).
 template <typename T>
@@ -585,6 +705,19 @@ VX_API int vx_diff_prepare(const void* proj, int dtype, long long stride, void* 
   if (num_tokens <= 0) return 0;
   if (2 * dim > D || vdim > D || rot > dim || (rot & 1)) return (int)cudaErrorInvalidValue;
   const int units = 2 * H + 2 * G + G;
+  const int pack = dtype == VX_DTYPE_F32 ? 4 : 8;
+  if (dim % pack == 0 && (rot / 2) % pack == 0 && vdim % pack == 0 && D % pack == 0 && stride % pack == 0 &&
+      q_stride % pack == 0 && dim / pack <= 32 && aligned16(proj) && aligned16(qbuf) && aligned16(cos_t) &&
+      aligned16(sin_t) && aligned16(q_norm) && aligned16(k_norm) && aligned16(k_cache) && aligned16(v_cache)) {
+    int gl = 1;
+    while (gl * pack < dim) gl *= 2;
+    const int per_block = 4 * (32 / gl);
+    const dim3 vec_grid(num_tokens, (units + per_block - 1) / per_block);
+    VX_BY_DTYPE(dtype, launch_pdl(diff_prepare_vec_kernel<T>, vec_grid, dim3(128), 0, stream, (const T*)proj, stride,
+                                  (T*)qbuf, q_stride, positions, cos_t, sin_t, q_norm, k_norm, eps, slots, (T*)k_cache,
+                                  (T*)v_cache, H, G, dim, vdim, D, rot, max_pos, num_slots, write_cache, status, gl));
+    return (int)cudaGetLastError();
+  }
   const dim3 grid(num_tokens, (units + 3) / 4);
   VX_BY_DTYPE(dtype, launch_pdl(diff_prepare_kernel<T>, grid, dim3(128), 0, stream, (const T*)proj, stride, (T*)qbuf,
                                 q_stride, positions, cos_t, sin_t, q_norm, k_norm, eps, slots, (T*)k_cache,
