@@ -78,7 +78,7 @@ ODD = config(100, 331, [
 # and a key tile, a loop over the middle that runs three times.
 WIDE = config(256, 500, [
     layer("attention", scored(8, 2, 64, 64, 0.125, q_temp=(0.2, 50)), dense(384, 1.5)),
-    layer("attention_2", differential(4, 1, 128, 96, 0.09, 0.5, chunk=150, rot=(1000000.0, 64), softcap=20.0),
+    layer("attention_2", differential(4, 1, 128, 96, 0.09, 0.45, chunk=150, rot=(500000.0, 64), softcap=20.0),
           dense(256, 1.0)),
     layer("attention_2", differential(8, 4, 32, 64, 0.18, 0.35, chunk=64, rot=(500.0, 32)), None),
     layer("attention", scored(4, 4, 128, 32, 0.09), dense(128, 3.0)),
