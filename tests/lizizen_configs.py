@@ -84,7 +84,16 @@ WIDE = config(256, 500, [
     layer("attention", scored(4, 4, 128, 32, 0.09), dense(128, 3.0)),
 ], eps=2e-5, loop=(1, 3, 3))
 
-ALL = {"small": SMALL, "odd": ODD, "wide": WIDE}
+# Head sizes between the common ones (cached rows of 80 and 112), rotated dims whose half is no
+# multiple of eight, a chunk that is no multiple of a page, three heads per KV head in both mixers,
+# a loop over the last two layers.
+MID = config(192, 700, [
+    layer("attention_2", differential(6, 2, 56, 40, 0.13, 0.4, chunk=100, rot=(300000.0, 24), softcap=40.0), dense(320, 1.2)),
+    layer("attention", scored(6, 2, 72, 72, 0.12, q_temp=(0.25, 64)), dense(200, 2.5)),
+    layer("attention_2", differential(3, 1, 40, 80, 0.16, 0.6, chunk=90, rot=(20000.0, 20)), dense(144)),
+], eps=1e-6, loop=(1, 3, 2))
+
+ALL = {"small": SMALL, "odd": ODD, "wide": WIDE, "mid": MID}
 
 
 def make_weights(cfg: Dict[str, Any], seed: int, sharp: float = 1.0) -> Dict[str, torch.Tensor]:

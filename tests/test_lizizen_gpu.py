@@ -357,6 +357,7 @@ CASES = {
     "small": (lc.SMALL, 4, (5, 11, 17, 60, 100), 2.0),
     "odd": (lc.ODD, 16, (1, 9, 33, 70, 150), 1.5),
     "wide": (lc.WIDE, 64, (130, 3, 65, 300, 64), 2.5),
+    "mid": (lc.MID, 16, (40, 2, 101, 230, 91), 2.0),
 }
 
 

@@ -73,7 +73,6 @@ class Attention(Mixer):
         if params.get("distance_bias", False):
             self.distance_bias = (self.expect("bias_r1", (self.num_heads,)), self.expect("bias_r2", (self.num_heads,)))
         self.row_scale = getattr(position, "row_scale", None)
-        self.scored = self.sink_zero or self.distance_bias is not None or self.row_scale is not None
         self.b_qkv = None
         self.b_qkv_lowp = None
         if "qkv.weight" in weights:
