@@ -844,6 +844,201 @@ class LizizenConfig(ModelConfig):
         return out
 
 
+def _rotation(m: Mapping[str, Any], where: str, limit: int, what: str):
+    """``rot`` = {base, dims[, scaling: {factor, original, fast, slow}]} -> (base, dims, scaling or None)."""
+    r = _mapping(m, "rot", where)
+    dims = _count(r, "dims", where + ".rot")
+    if dims % 2 or dims > limit:
+        raise ConfigError(f"{where}.rot: dims={dims} must be even and at most {what}={limit}")
+    scaling = None
+    if r.get("scaling") is not None:
+        sc = _mapping(r, "scaling", where + ".rot")
+        scaling = tuple(_number(sc, key, where + ".rot.scaling") for key in ("factor", "original", "fast", "slow"))
+        if min(scaling) <= 0:
+            raise ConfigError(f"{where}.rot.scaling: factor, original, fast and slow must be positive")
+    base = _number(r, "base", where + ".rot")
+    if base <= 1.0:
+        raise ConfigError(f"{where}.rot: base={base} must be above 1")
+    return base, dims, scaling
+
+
+def _rotation_json(rot) -> Dict[str, Any]:
+    base, dims, scaling = rot
+    out: Dict[str, Any] = {"base": base, "dims": dims}
+    if scaling is not None:
+        out["scaling"] = dict(zip(("factor", "original", "fast", "slow"), scaling))
+    return out
+
+
+@dataclass(frozen=True)
+class WindowedLatentConfig:
+    """Latent attention over a sliding window: ``heads`` heads of ``dim`` unrotated and ``rot_dim``
+    rotated query/key dims and ``vdim`` value dims over a cached latent of ``kv_rank`` values; the
+    queries come through a normed latent of ``q_rank`` values; ``rot`` = (base, dims, scaling or
+    None) turns the rotated part in halves; a learned sink per head joins the softmax denominator
+    and the heads' outputs pass an element-wise gate."""
+
+    heads: int
+    dim: int
+    rot_dim: int
+    vdim: int
+    kv_rank: int
+    q_rank: int
+    scale: float
+    window: int
+    rot: Tuple[float, int, Optional[Tuple[float, float, float, float]]]
+
+    @staticmethod
+    def parse(m: Mapping[str, Any], where: str) -> "WindowedLatentConfig":
+        rot_dim = _count(m, "rot_dim", where)
+        rot = _rotation(m, where, rot_dim, "rot_dim")
+        if rot[1] != rot_dim:
+            raise ConfigError(f"{where}.rot: dims={rot[1]} must equal rot_dim={rot_dim} (the whole rotated part turns)")
+        window, _ = _window(m, where, keep_allowed=False)
+        return WindowedLatentConfig(
+            heads=_count(m, "heads", where), dim=_count(m, "dim", where), rot_dim=rot_dim, vdim=_count(m, "vdim", where),
+            kv_rank=_count(m, "kv_rank", where), q_rank=_count(m, "q_rank", where), scale=_number(m, "scale", where),
+            window=window, rot=rot)
+
+    def to_json_dict(self) -> Dict[str, Any]:
+        return {"heads": self.heads, "dim": self.dim, "rot_dim": self.rot_dim, "vdim": self.vdim,
+                "kv_rank": self.kv_rank, "q_rank": self.q_rank, "scale": self.scale, "mask": {"size": self.window},
+                "rot": _rotation_json(self.rot)}
+
+
+@dataclass(frozen=True)
+class DeltaRuleConfig:
+    """The generalized delta rule: ``heads`` heads whose state is ``dim`` x ``dim``."""
+
+    heads: int
+    dim: int
+
+    @staticmethod
+    def parse(m: Mapping[str, Any], where: str) -> "DeltaRuleConfig":
+        return DeltaRuleConfig(heads=_count(m, "heads", where), dim=_count(m, "dim", where))
+
+    def to_json_dict(self) -> Dict[str, Any]:
+        return {"heads": self.heads, "dim": self.dim}
+
+
+@dataclass(frozen=True)
+class GatedFeedForwardConfig:
+    """A gated feed-forward of inner width ``ff``."""
+
+    ff: int
+
+    @staticmethod
+    def parse(m: Mapping[str, Any], where: str) -> "GatedFeedForwardConfig":
+        kind = m.get("kind")
+        if kind != "dense":
+            raise ConfigError(f"{where}: mlp kind {kind!r} is not supported ('dense' is)")
+        return GatedFeedForwardConfig(ff=_count(m, "ff", where))
+
+    def to_json_dict(self) -> Dict[str, Any]:
+        return {"kind": "dense", "ff": self.ff}
+
+
+@dataclass(frozen=True)
+class MamivikLayerConfig:
+    """``type`` latent_attention: ``latent``; parallel: ``left`` (attention whose values are its
+    keys) and ``right`` (delta rule), summed with ``left_scale`` and ``right_scale``."""
+
+    type: str
+    latent: Optional[WindowedLatentConfig] = None
+    left: Optional[WindowAttentionConfig] = None
+    right: Optional[DeltaRuleConfig] = None
+    left_scale: float = 1.0
+    right_scale: float = 1.0
+    mlp: Optional[GatedFeedForwardConfig] = None
+
+
+@dataclass(frozen=True)
+class MamivikConfig(ModelConfig):
+    """``Mamivik``: pre-norm layers ``x <- x + mixer(h + conv(h))`` with ``h = norm1(x)`` and a
+    causal convolution of ``canon_taps`` taps per channel, then ``x <- x + ff(norm2(x))``; every
+    norm is an RMS norm times one number.  The mixer is latent attention over a window with a
+    sink and an output gate (``latent_attention``), or windowed attention whose values are its
+    unrotated keys beside a generalized delta rule (``parallel``); the feed-forward is gated with
+    the tanh form of GELU.  config.json keys: ``vocab``, ``width``, ``norm.eps``, ``canon.taps``
+    and ``layers`` (a list of ``{type, mixer, mlp}``)."""
+
+    layers: Tuple[MamivikLayerConfig, ...] = ()
+    norm_eps: float = 1e-5
+    canon_taps: int = 1
+    torch_dtype: str = "bfloat16"
+
+    @staticmethod
+    def from_dict(cfg: Mapping[str, Any]) -> "MamivikConfig":
+        name = cfg.get("architecture") or (cfg.get("architectures") or ["Mamivik"])[0]
+        raw_layers = cfg.get("layers")
+        if not isinstance(raw_layers, (list, tuple)) or not raw_layers:
+            raise ConfigError("config.json key 'layers' must be a non-empty list")
+        layers = []
+        for index, raw in enumerate(raw_layers):
+            where = f"config.json layers[{index}]"
+            if not isinstance(raw, Mapping):
+                raise ConfigError(f"{where} must be an object")
+            kind = raw.get("type")
+            m = _mapping(raw, "mixer", where)
+            mlp = None
+            if raw.get("mlp") is not None:
+                mlp = GatedFeedForwardConfig.parse(_mapping(raw, "mlp", where), where + ".mlp")
+            if kind == "latent_attention":
+                layer = MamivikLayerConfig(type=kind, latent=WindowedLatentConfig.parse(m, where + ".mixer"), mlp=mlp)
+            elif kind == "parallel":
+                left = WindowAttentionConfig.parse(_mapping(m, "left", where + ".mixer"), where + ".mixer.left",
+                                                   rotated=True, biases=True, sink=False, head_gate=False,
+                                                   keep_allowed=False)
+                if left.vdim != left.dim:
+                    raise ConfigError(f"{where}.mixer.left: the values are the keys, so vdim={left.vdim} must equal "
+                                      f"dim={left.dim}")
+                layer = MamivikLayerConfig(
+                    type=kind, left=left,
+                    right=DeltaRuleConfig.parse(_mapping(m, "right", where + ".mixer"), where + ".mixer.right"),
+                    left_scale=_number(m, "left_scale", where + ".mixer"),
+                    right_scale=_number(m, "right_scale", where + ".mixer"), mlp=mlp)
+            else:
+                raise ConfigError(f"{where}: layer type {kind!r} is not supported "
+                                  "('latent_attention' and 'parallel' are)")
+            layers.append(layer)
+        eos = cfg.get("eos_token_id")
+        eos_ids: Tuple[int, ...] = () if eos is None else ((eos,) if isinstance(eos, int) else tuple(int(t) for t in eos))
+        return MamivikConfig(
+            architecture=str(name),
+            vocab_size=_count(cfg, "vocab", "config.json"),
+            hidden_size=_count(cfg, "width", "config.json"),
+            num_hidden_layers=len(layers),
+            max_position_embeddings=int(cfg.get("max_position_embeddings", 1 << 20)),
+            tie_word_embeddings=False,
+            eos_token_ids=eos_ids,
+            layers=tuple(layers),
+            norm_eps=_number(_mapping(cfg, "norm", "config.json"), "eps", "config.json norm"),
+            canon_taps=_count(_mapping(cfg, "canon", "config.json"), "taps", "config.json canon"),
+            torch_dtype=str(cfg.get("torch_dtype", "bfloat16")),
+        )
+
+    def to_json_dict(self) -> Dict[str, Any]:
+        layers = []
+        for layer in self.layers:
+            if layer.type == "parallel":
+                mixer: Dict[str, Any] = {"left": layer.left.to_json_dict(), "right": layer.right.to_json_dict(),
+                                         "left_scale": layer.left_scale, "right_scale": layer.right_scale}
+            else:
+                mixer = layer.latent.to_json_dict()
+            layers.append({"type": layer.type, "mixer": mixer,
+                           "mlp": None if layer.mlp is None else layer.mlp.to_json_dict()})
+        out: Dict[str, Any] = {
+            "architecture": self.architecture, "vocab": self.vocab_size, "width": self.hidden_size,
+            "norm": {"eps": self.norm_eps}, "canon": {"taps": self.canon_taps}, "layers": layers,
+            "torch_dtype": self.torch_dtype,
+        }
+        if self.max_position_embeddings != 1 << 20:
+            out["max_position_embeddings"] = self.max_position_embeddings
+        if self.eos_token_ids:
+            out["eos_token_id"] = list(self.eos_token_ids)
+        return out
+
+
 def read_config_json(model_dir: str) -> Dict[str, Any]:
     path = os.path.join(model_dir, "config.json")
     if not os.path.isfile(path):

@@ -7,7 +7,7 @@ registry: ``Engine.from_pretrained`` hard-codes its one model class (engine/engi
 from __future__ import annotations
 
 from dataclasses import dataclass
-from typing import Any, Callable, Dict, Mapping
+from typing import Any, Callable, Dict, Mapping, Optional
 
 from .model_config import ConfigError, ModelConfig, read_config_json
 
@@ -16,7 +16,11 @@ from .model_config import ConfigError, ModelConfig, read_config_json
 class Architecture:
     name: str
     parse_config: Callable[[Mapping[str, Any]], ModelConfig]
-    build_spec: Callable[[ModelConfig], Any]
+    build_spec: Callable[..., Any]
+    # Sizes that no configuration key names and only a checkpoint's tensor shapes give:
+    # ``checkpoint_sizes(config, shape_of)`` (``shape_of(name)`` is a tensor's shape or None) returns
+    # keyword arguments for ``build_spec``.  None: the configuration says everything.
+    checkpoint_sizes: Optional[Callable[..., Dict[str, Any]]] = None
 
 
 _ARCHITECTURES: Dict[str, Architecture] = {}
@@ -25,9 +29,10 @@ _ARCHITECTURES: Dict[str, Architecture] = {}
 def register_architecture(
     name: str,
     parse_config: Callable[[Mapping[str, Any]], ModelConfig],
-    build_spec: Callable[[ModelConfig], Any],
+    build_spec: Callable[..., Any],
+    checkpoint_sizes: Optional[Callable[..., Dict[str, Any]]] = None,
 ) -> None:
-    _ARCHITECTURES[name] = Architecture(name, parse_config, build_spec)
+    _ARCHITECTURES[name] = Architecture(name, parse_config, build_spec, checkpoint_sizes)
 
 
 def unregister_architecture(name: str) -> None:

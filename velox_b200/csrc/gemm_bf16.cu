@@ -188,14 +188,15 @@ struct GemmArgs {
   long long ld2;
   // Mode 3: with g = gate + bias[n] and u = up + bias[N + n] (bias [2 N] or null),
   //   g <- min(g, glu_limit), u <- clamp(u, -glu_limit, glu_limit)   (glu_limit > 0)
-  //   out = g * sigmoid(glu_alpha * g) * (u + glu_shift)
-  // glu_alpha 1, glu_shift 0 and no limit: silu(gate) * up.
-  float glu_limit, glu_alpha, glu_shift;
+  //   out = g * sigmoid(glu_alpha * (g + glu_cubic * g^3)) * (u + glu_shift)
+  // glu_alpha 1, glu_cubic 0, glu_shift 0 and no limit: silu(gate) * up.  glu_alpha 2 sqrt(2 / pi)
+  // and glu_cubic 0.044715: the tanh form of GELU, since (1 + tanh(y)) / 2 = sigmoid(2 y).
+  float glu_limit, glu_alpha, glu_shift, glu_cubic;
 };
 
 // The gated activation of mode 3 with its options.
 struct GluArgs {
-  float limit, alpha, shift;
+  float limit, alpha, shift, cubic;
 };
 
 __device__ __forceinline__ void cluster_arrive() {
@@ -565,8 +566,9 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constan
                   gate = fminf(gate, g.glu_limit);
                   up = fminf(fmaxf(up, -g.glu_limit), g.glu_limit);
                 }
+                const float bent = fmaf(g.glu_cubic * gate, gate * gate, gate);
                 out[(size_t)t * g.ldy + n] =
-                    __float2bfloat16_rn(gate / (1.0f + __expf(-g.glu_alpha * gate)) * (up + g.glu_shift));
+                    __float2bfloat16_rn(gate / (1.0f + __expf(-g.glu_alpha * bent)) * (up + g.glu_shift));
               }
             }
           }
@@ -1298,6 +1300,7 @@ static int gemm_bf16(const void* x, int x_rows, const float* resid, long long re
   g.glu_limit = glu != nullptr && glu->limit > 0.f ? glu->limit : 0.f;
   g.glu_alpha = glu != nullptr ? glu->alpha : 1.0f;
   g.glu_shift = glu != nullptr ? glu->shift : 0.f;
+  g.glu_cubic = glu != nullptr ? glu->cubic : 0.f;
   g.kb_per_split = (num_kb + splits - 1) / splits;
   g.splits = splits;
   // K in chunks of independent CTAs (mode 2 only): every CTA adds its partial tile to the output
@@ -1396,8 +1399,9 @@ VX_API int vx_gemm_bf16(const void* x, const void* w, const float* bias, void* o
 // Mode 3 with the options of the gated activation (see GemmArgs): w [2 N, K] holds the N gate rows
 // and then the N up rows, bias [2 N] (or null) alike; out bf16 [T, ldy] has N columns.
 VX_API int vx_gemm_bf16_glu(const void* x, const void* w, const float* bias, void* out, int T, int x_rows, int N, int K,
-                            long long ldy, float limit, float alpha, float shift, int* status, cudaStream_t stream) {
-  const GluArgs glu = {limit, alpha, shift};
+                            long long ldy, float limit, float alpha, float shift, float cubic, int* status,
+                            cudaStream_t stream) {
+  const GluArgs glu = {limit, alpha, shift, cubic};
   return gemm_bf16(x, x_rows, nullptr, 0, nullptr, 0.f, w, bias, out, 3, T, N, K, ldy, 1, status, stream, nullptr,
                    nullptr, 0, 1, nullptr, &glu);
 }

@@ -4,14 +4,18 @@
 //   norm_shift_kernel        one RMS statistic per row, two weighted outputs; the first output is
 //                            mixed with the previous token's (token shift), whose last value per
 //                            request lives in a slot-indexed state row
-//   add_rows_kernel          stream += a (+ b), float32 sums
+//   norm_conv_kernel         RMS norm, then h + a causal convolution of h over the request's
+//                            tokens per channel; the last taps - 1 values of h per request live
+//                            in a slot-indexed state row
+//   add_rows_kernel          stream += scale_a * a (+ scale_b * b), float32 sums
 //   diff_prepare_kernel      differential attention: per (head, map) RMS norm of q and k, rotation
 //                            of the first dims of every map, q into a buffer whose "heads" are
 //                            (head, map) pairs with the map's dims at the map's offset, k of both
 //                            maps side by side into one cached row, v into its page
 //   diff_combine_kernel      o = a1 - lambda a2, unit RMS over the head, times (1 - lambda_init),
 //                            times sigmoid(gate)
-//   clamped_glu_kernel       g = min(g, limit), u = clamp(u, +-limit), g sigmoid(alpha g) (u + shift)
+//   clamped_glu_kernel       g = min(g, limit), u = clamp(u, +-limit),
+//                            g sigmoid(alpha (g + cubic g^3)) (u + shift)
 //
 // Everything between the loads and the stores is float32.  Every sum has an order that depends
 // on the sizes only.
@@ -128,6 +132,107 @@ __global__ void norm_shift_kernel(const float* __restrict__ resid, long long res
     const float lr = rsqrtf(block_sum(ls, scratch) / (float)width + eps);
     float* dst = state + (size_t)seq_slots[seq] * state_stride;
     for (int i = threadIdx.x; i < width; i += blockDim.x) dst[i] = xl[i] * lr * w1[i];
+  }
+}
+
+// ---------------------------------------------------------------------------------------------
+// Input convolution.  With h_t = x_t / rms(x_t) * w the output of row t is
+//     h_t + sum_j cw[:, j] * h_(t - taps + 1 + j),   j = 0 .. taps - 1
+// over the request's own tokens, zeros before its first token.  h of a token of this step is
+// recomputed from its row of the stream; h of the taps - 1 tokens before the portion comes from the
+// request's state row [(taps - 1) x width] (oldest first; zero when a slot is taken).  A value of h
+// is the same float whether it was recomputed or stored: one order of the row's sum, and the
+// products x * r * w made one by one.
+// One block per row, except the first taps - 1 rows of a portion: the block of the portion's first
+// row makes them all, and then writes the portion's last taps - 1 values of h into the state row
+// (entries of a portion shorter than that move up), so nobody else reads or writes the row.
+constexpr int NC_MAX_TAPS = 8;
+
+__device__ __forceinline__ float nc_value(float x, float r, float w) { return __fmul_rn(__fmul_rn(x, r), w); }
+
+__device__ __forceinline__ float nc_inverse_rms(const float* __restrict__ x, int width, float eps, float* scratch) {
+  float ss = 0.f;
+  for (int i = threadIdx.x; i < width; i += blockDim.x) ss = fmaf(x[i], x[i], ss);
+  return rsqrtf(block_sum(ss, scratch) / (float)width + eps);
+}
+
+// Row `row` of a portion that starts at stream row `first`: its taps inputs come from the stream
+// (portion index >= 0) or from the old state.
+template <typename T>
+__device__ __forceinline__ void nc_row(const float* __restrict__ resid, long long resid_stride, int width, float eps,
+                                       const float* __restrict__ w, const float* __restrict__ cw, int taps,
+                                       const float* old_state, int first, int row,
+                                       T* __restrict__ out, float* scratch) {
+  float r[NC_MAX_TAPS];
+#pragma unroll
+  for (int j = 0; j < NC_MAX_TAPS; ++j) {
+    r[j] = 0.f;
+    if (j < taps) {
+      const int src = row - (taps - 1) + j;
+      if (src >= 0) r[j] = nc_inverse_rms(resid + (size_t)(first + src) * resid_stride, width, eps, scratch);
+    }
+  }
+  for (int i = threadIdx.x; i < width; i += blockDim.x) {
+    float h = 0.f, acc = 0.f;
+#pragma unroll
+    for (int j = 0; j < NC_MAX_TAPS; ++j) {
+      if (j < taps) {
+        const int src = row - (taps - 1) + j;
+        if (src >= 0) h = nc_value(resid[(size_t)(first + src) * resid_stride + i], r[j], w[i]);
+        else h = old_state != nullptr ? old_state[(size_t)(row + j) * width + i] : 0.f;
+        acc = fmaf(cw[(size_t)i * taps + j], h, acc);
+      }
+    }
+    // h is now the row's own value (j = taps - 1).
+    out[(size_t)(first + row) * width + i] = from_float<T>(h + acc);
+  }
+}
+
+template <typename T>
+__global__ void norm_conv_kernel(const float* __restrict__ resid, long long resid_stride, int width, float eps,
+                                 const float* __restrict__ w, const float* __restrict__ cw, int taps,
+                                 float* state, long long state_stride, T* __restrict__ out,
+                                 const int* __restrict__ q_start, const int* __restrict__ q_len,
+                                 const int* __restrict__ seq_slots, int num_seqs) {
+  __shared__ float scratch[32];
+  allow_dependents();
+  const int t = blockIdx.x;
+  int seq = -1, first = t, count = 1;
+  for (int s = 0; s < num_seqs; ++s) {
+    const int b = q_start[s], n = q_len[s];
+    if (n > 0 && t >= b && t < b + n) {
+      seq = s;
+      first = b;
+      count = n;
+    }
+  }
+  grid_dependency_wait();
+  const int row = t - first;
+  if (seq < 0) {
+    // A row of no request (padding of a rounded step): no history; nobody looks at it.
+    nc_row<T>(resid, resid_stride, width, eps, w, cw, taps, nullptr, t, 0, out, scratch);
+    return;
+  }
+  if (row >= taps - 1) {
+    nc_row<T>(resid, resid_stride, width, eps, w, cw, taps, nullptr, first, row, out, scratch);
+    return;
+  }
+  if (row != 0) return;  // made by the block of the portion's first row
+  float* mine = state + (size_t)seq_slots[seq] * state_stride;
+  const int head_rows = min(taps - 1, count);
+  for (int i = 0; i < head_rows; ++i)
+    nc_row<T>(resid, resid_stride, width, eps, w, cw, taps, mine, first, i, out, scratch);
+  // New state: entry e is h of portion index count - (taps - 1) + e; a negative index is the old
+  // entry count + e, which lies above e, and a thread moves its own channels in rising e.
+  for (int e = 0; e < taps - 1; ++e) {
+    const int src = count - (taps - 1) + e;
+    if (src >= 0) {
+      const float* x = resid + (size_t)(first + src) * resid_stride;
+      const float r = nc_inverse_rms(x, width, eps, scratch);
+      for (int i = threadIdx.x; i < width; i += blockDim.x) mine[(size_t)e * width + i] = nc_value(x[i], r, w[i]);
+    } else {
+      for (int i = threadIdx.x; i < width; i += blockDim.x) mine[(size_t)e * width + i] = mine[(size_t)(count + e) * width + i];
+    }
   }
 }
 
@@ -256,20 +361,20 @@ __global__ void norm_shift_vec_kernel(const float* __restrict__ resid, long long
 
 template <typename T>
 __global__ void add_rows_kernel(float* __restrict__ resid, const T* __restrict__ a, const T* __restrict__ b,
-                                long long count) {
+                                long long count, float scale_a, float scale_b) {
   allow_dependents();
   grid_dependency_wait();
   for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < count;
        i += (long long)gridDim.x * blockDim.x) {
-    float v = resid[i] + to_float(a[i]);
-    if (b != nullptr) v += to_float(b[i]);
+    float v = resid[i] + scale_a * to_float(a[i]);
+    if (b != nullptr) v += scale_b * to_float(b[i]);
     resid[i] = v;
   }
 }
 
 template <typename T>
 __global__ void add_rows_vec_kernel(float* __restrict__ resid, const T* __restrict__ a, const T* __restrict__ b,
-                                    long long packs) {
+                                    long long packs, float scale_a, float scale_b) {
   constexpr int N = Pack<T>::N;
   allow_dependents();
   grid_dependency_wait();
@@ -278,10 +383,12 @@ __global__ void add_rows_vec_kernel(float* __restrict__ resid, const T* __restri
     const long long i = p * N;
     float av[N], bv[N];
     load_pack(a + i, av);
+#pragma unroll
+    for (int e = 0; e < N; ++e) av[e] *= scale_a;
     if (b != nullptr) {
       load_pack(b + i, bv);
 #pragma unroll
-      for (int e = 0; e < N; ++e) av[e] += bv[e];
+      for (int e = 0; e < N; ++e) av[e] += scale_b * bv[e];
     }
 #pragma unroll
     for (int j = 0; j < N; j += 4) {
@@ -593,7 +700,7 @@ __global__ void diff_combine_vec_kernel(const T* __restrict__ attn, long long at
 template <typename T>
 __global__ void clamped_glu_kernel(const T* __restrict__ gate_up, long long in_stride, T* __restrict__ out,
                                    long long out_stride, int F, float limit, float alpha, float up_shift,
-                                   long long count) {
+                                   float cubic, long long count) {
   allow_dependents();
   grid_dependency_wait();
   for (long long idx = (long long)blockIdx.x * blockDim.x + threadIdx.x; idx < count;
@@ -606,14 +713,15 @@ __global__ void clamped_glu_kernel(const T* __restrict__ gate_up, long long in_s
       g = fminf(g, limit);
       u = fminf(fmaxf(u, -limit), limit);
     }
-    out[t * out_stride + f] = from_float<T>(g * hd_sigmoid(alpha * g) * (u + up_shift));
+    out[t * out_stride + f] = from_float<T>(g * hd_sigmoid(alpha * fmaf(cubic * g, g * g, g)) * (u + up_shift));
   }
 }
 
 // The same, sixteen bytes of gate and of up per thread (F and both pitches multiples of the pack).
 template <typename T>
 __global__ void clamped_glu_vec_kernel(const T* __restrict__ gate_up, long long in_stride, T* __restrict__ out,
-                                       long long out_stride, int F, float limit, float alpha, float up_shift) {
+                                       long long out_stride, int F, float limit, float alpha, float up_shift,
+                                       float cubic) {
   constexpr int N = Pack<T>::N;
   allow_dependents();
   grid_dependency_wait();
@@ -630,7 +738,7 @@ __global__ void clamped_glu_vec_kernel(const T* __restrict__ gate_up, long long 
         gv = fminf(gv, limit);
         uv = fminf(fmaxf(uv, -limit), limit);
       }
-      g[e] = gv * sigmoid_for<T>(alpha * gv) * (uv + up_shift);
+      g[e] = gv * sigmoid_for<T>(alpha * fmaf(cubic * gv, gv * gv, gv)) * (uv + up_shift);
     }
     store_pack(dst + f, g);
   }
@@ -679,7 +787,21 @@ VX_API int vx_norm_shift(const float* resid, long long resid_stride, int width, 
   return (int)cudaGetLastError();
 }
 
-VX_API int vx_add_rows(float* resid, const void* a, const void* b, int dtype, long long count, cudaStream_t stream) {
+VX_API int vx_norm_conv(const float* resid, long long resid_stride, int width, float eps, const float* w,
+                        const float* conv_w, int taps, float* state, long long state_stride, void* out, int dtype,
+                        const int* q_start, const int* q_len, const int* seq_slots, int num_seqs, int num_tokens,
+                        cudaStream_t stream) {
+  if (num_tokens <= 0) return 0;
+  if (taps < 1 || taps > NC_MAX_TAPS) return -1;
+  if (taps > 1 && (state == nullptr || state_stride < (long long)(taps - 1) * width)) return (int)cudaErrorInvalidValue;
+  VX_BY_DTYPE(dtype, launch_pdl(norm_conv_kernel<T>, dim3(num_tokens), dim3(row_threads(width)), 0, stream, resid,
+                                resid_stride, width, eps, w, conv_w, taps, state, state_stride, (T*)out, q_start,
+                                q_len, seq_slots, num_seqs));
+  return (int)cudaGetLastError();
+}
+
+VX_API int vx_add_rows(float* resid, const void* a, const void* b, int dtype, long long count, float scale_a,
+                       float scale_b, cudaStream_t stream) {
   if (count <= 0) return 0;
   const int pack = dtype == VX_DTYPE_F32 ? 4 : 8;
   if (count % pack == 0 && aligned16(resid) && aligned16(a) && aligned16(b)) {
@@ -687,13 +809,13 @@ VX_API int vx_add_rows(float* resid, const void* a, const void* b, int dtype, lo
     long long vec_blocks = (packs + 255) / 256;
     if (vec_blocks > 148 * 8) vec_blocks = 148 * 8;
     VX_BY_DTYPE(dtype, launch_pdl(add_rows_vec_kernel<T>, dim3((unsigned)vec_blocks), dim3(256), 0, stream, resid,
-                                  (const T*)a, (const T*)b, packs));
+                                  (const T*)a, (const T*)b, packs, scale_a, scale_b));
     return (int)cudaGetLastError();
   }
   long long blocks = (count + 255) / 256;
   if (blocks > 148 * 16) blocks = 148 * 16;
   VX_BY_DTYPE(dtype, launch_pdl(add_rows_kernel<T>, dim3((unsigned)blocks), dim3(256), 0, stream, resid,
-                                (const T*)a, (const T*)b, count));
+                                (const T*)a, (const T*)b, count, scale_a, scale_b));
   return (int)cudaGetLastError();
 }
 
@@ -745,7 +867,8 @@ VX_API int vx_diff_combine(const void* attn, int dtype, long long attn_stride, c
 }
 
 VX_API int vx_clamped_glu(const void* gate_up, int dtype, long long in_stride, void* out, long long out_stride,
-                          int num_tokens, int F, float limit, float alpha, float up_shift, cudaStream_t stream) {
+                          int num_tokens, int F, float limit, float alpha, float up_shift, float cubic,
+                          cudaStream_t stream) {
   if (num_tokens <= 0 || F <= 0) return 0;
   const int pack = dtype == VX_DTYPE_F32 ? 4 : 8;
   if (F % pack == 0 && in_stride % pack == 0 && out_stride % pack == 0 && aligned16(gate_up) && aligned16(out) &&
@@ -754,14 +877,14 @@ VX_API int vx_clamped_glu(const void* gate_up, int dtype, long long in_stride, v
     int across = (F / pack + threads - 1) / threads;
     if (across > 32) across = 32;
     VX_BY_DTYPE(dtype, launch_pdl(clamped_glu_vec_kernel<T>, dim3(across, num_tokens), dim3(threads), 0, stream,
-                                  (const T*)gate_up, in_stride, (T*)out, out_stride, F, limit, alpha, up_shift));
+                                  (const T*)gate_up, in_stride, (T*)out, out_stride, F, limit, alpha, up_shift, cubic));
     return (int)cudaGetLastError();
   }
   const long long count = (long long)num_tokens * F;
   long long blocks = (count + 255) / 256;
   if (blocks > 148 * 16) blocks = 148 * 16;
   VX_BY_DTYPE(dtype, launch_pdl(clamped_glu_kernel<T>, dim3((unsigned)blocks), dim3(256), 0, stream,
-                                (const T*)gate_up, in_stride, (T*)out, out_stride, F, limit, alpha, up_shift, count));
+                                (const T*)gate_up, in_stride, (T*)out, out_stride, F, limit, alpha, up_shift, cubic, count));
   return (int)cudaGetLastError();
 }
 

@@ -21,8 +21,8 @@
 //
 // Rotation: dims 2i and 2i + 1 of the first 2 * rot_pairs dims are a pair (u, v) ->
 // (u cos a - v sin a, v cos a + u sin a), a = position * base^(-2i / (2 rot_pairs)); cos and sin
-// come from float32 tables [max_pos, rot_pairs].  Norm, rotation, sigmoid and all sums are
-// float32.
+// come from float32 tables [max_pos, rot_pairs].  With `half_layout` the pair is dims i and
+// i + rot_pairs instead.  Norm, rotation, sigmoid and all sums are float32.
 #include "common.cuh"
 
 namespace vx {
@@ -30,25 +30,35 @@ namespace vx {
 template <typename T>
 __device__ __forceinline__ float rotated_interleaved(const T* __restrict__ x, int j, int rot_pairs,
                                                      const float* __restrict__ cos_row,
-                                                     const float* __restrict__ sin_row) {
+                                                     const float* __restrict__ sin_row, int half_layout = 0) {
   if (j >= 2 * rot_pairs) return to_float(x[j]);
+  if (half_layout) {
+    const bool second = j >= rot_pairs;
+    const int i = second ? j - rot_pairs : j;
+    const float u = to_float(x[i]), v = to_float(x[i + rot_pairs]);
+    const float c = cos_row[i], s = sin_row[i];
+    return second ? fmaf(v, c, u * s) : fmaf(u, c, -(v * s));
+  }
   const int i = j >> 1;
   const float u = to_float(x[2 * i]), v = to_float(x[2 * i + 1]);
   const float c = cos_row[i], s = sin_row[i];
   return (j & 1) ? fmaf(v, c, u * s) : fmaf(u, c, -(v * s));
 }
 
-// proj [T, proj_ld]: q head h at q_off + h * (dim + R), its last R dims rotate; the token's own
+// proj [T, proj_ld]: q head h at q_off + h * (dim + R), its last R dims rotate (or, when the
+// queries come from a projection of their own, in q_src [T, q_ld] at the same offset); the token's own
 // latent (kr values, then R values of the shared key part) at dkv_off, or dkv_off < 0 for a layer
 // that reads another layer's cache.  qa [T, H, Dp]: [kr absorbed dims (written elsewhere) | R
 // rotated dims | zero pad].  cache [slots, Dp].
 template <typename T>
-__global__ void latent_prepare_kernel(const T* __restrict__ proj, long long proj_ld, int q_off, int dkv_off,
+__global__ void latent_prepare_kernel(const T* __restrict__ proj, long long proj_ld, const T* __restrict__ q_src,
+                                      long long q_ld, int q_off, int dkv_off,
                                       const int* __restrict__ positions, const float* __restrict__ cos_t,
                                       const float* __restrict__ sin_t, int max_pos, int rot_pairs,
                                       const float* __restrict__ latent_w, float eps,
                                       const int* __restrict__ slots, T* __restrict__ cache, long long num_slots,
-                                      T* __restrict__ qa, int H, int dim, int R, int kr, int Dp, int* status) {
+                                      T* __restrict__ qa, int H, int dim, int R, int kr, int Dp, int half_layout,
+                                      int* status) {
   __shared__ float scratch[32];
   allow_dependents();
   grid_dependency_wait();
@@ -61,11 +71,12 @@ __global__ void latent_prepare_kernel(const T* __restrict__ proj, long long proj
   const float* cos_row = cos_t + (size_t)pos * rot_pairs;
   const float* sin_row = sin_t + (size_t)pos * rot_pairs;
   const T* row = proj + (size_t)t * proj_ld;
+  const T* q_row = q_src != nullptr ? q_src + (size_t)t * q_ld : row;
   const int tail = Dp - kr;
   for (int idx = threadIdx.x; idx < H * tail; idx += blockDim.x) {
     const int h = idx / tail, j = idx - h * tail;
     float v = 0.f;
-    if (j < R) v = rotated_interleaved(row + q_off + (size_t)h * (dim + R) + dim, j, rot_pairs, cos_row, sin_row);
+    if (j < R) v = rotated_interleaved(q_row + q_off + (size_t)h * (dim + R) + dim, j, rot_pairs, cos_row, sin_row, half_layout);
     qa[((size_t)t * H + h) * Dp + kr + j] = from_float<T>(v);
   }
   if (dkv_off < 0) return;
@@ -87,13 +98,34 @@ __global__ void latent_prepare_kernel(const T* __restrict__ proj, long long proj
   for (int i = threadIdx.x; i < Dp; i += blockDim.x) {
     float v = 0.f;
     if (i < kr) v = to_float(lat[i]) * inv * latent_w[i];
-    else if (i < kr + R) v = rotated_interleaved(lat + kr, i - kr, rot_pairs, cos_row, sin_row);
+    else if (i < kr + R) v = rotated_interleaved(lat + kr, i - kr, rot_pairs, cos_row, sin_row, half_layout);
     dst[i] = from_float<T>(v);
   }
 }
 
+// out[t, i] = x[t, i] / sqrt(mean_i(x[t, :n]^2) + eps) * w[i] for i < n, zero for n <= i < n_out:
+// the RMS norm of a column range of a projection (a latent on the way to its second projection).
+template <typename T>
+__global__ void rms_rows_kernel(const T* __restrict__ x, long long x_ld, const float* __restrict__ w, float eps, int n,
+                                T* __restrict__ out, long long out_ld, int n_out) {
+  __shared__ float scratch[32];
+  allow_dependents();
+  grid_dependency_wait();
+  const T* row = x + (size_t)blockIdx.x * x_ld;
+  float ss = 0.f;
+  for (int i = threadIdx.x; i < n; i += blockDim.x) {
+    const float v = to_float(row[i]);
+    ss = fmaf(v, v, ss);
+  }
+  const float inv = 1.0f / sqrtf(block_sum(ss, scratch) / (float)n + eps);
+  T* dst = out + (size_t)blockIdx.x * out_ld;
+  for (int i = threadIdx.x; i < n_out; i += blockDim.x)
+    dst[i] = from_float<T>(i < n ? to_float(row[i]) * inv * w[i] : 0.f);
+}
+
 // out[t * out_ld + h * out_hs + n] = sum_k x[t * x_ld + h * x_hs + k] * w[(h * N + n) * K + k]
-//                                    (* sigmoid(gate[t * gate_ld + h]) with a gate)
+//                                    (* sigmoid(gate[t * gate_ld + h]) with a gate, or with
+//                                     `gate_each` * sigmoid(gate[t * gate_ld + h * N + n]))
 // One block per (tile of HL_TOKENS tokens, head); the tile's inputs are staged in shared memory
 // as float32, a warp takes output n and its lanes split k, so a weight row is read once per
 // block, coalesced.  Every output is summed in an order that depends on K only.
@@ -103,7 +135,7 @@ template <typename T>
 __global__ void __launch_bounds__(256)
 headwise_linear_kernel(const T* __restrict__ x, long long x_ld, int x_hs, const T* __restrict__ w,
                        T* __restrict__ out, long long out_ld, int out_hs, const T* __restrict__ gate,
-                       long long gate_ld, int num_tokens, int N, int K) {
+                       long long gate_ld, int num_tokens, int N, int K, int gate_each) {
   extern __shared__ float xs[];  // [HL_TOKENS][K]
   allow_dependents();
   grid_dependency_wait();
@@ -119,7 +151,8 @@ headwise_linear_kernel(const T* __restrict__ x, long long x_ld, int x_hs, const 
 #pragma unroll
   for (int r = 0; r < HL_TOKENS; ++r) {
     const int t = t0 + r;
-    g[r] = (gate != nullptr && t < num_tokens) ? 1.0f / (1.0f + expf(-to_float(gate[(size_t)t * gate_ld + h]))) : 1.0f;
+    g[r] = (gate != nullptr && !gate_each && t < num_tokens)
+               ? 1.0f / (1.0f + expf(-to_float(gate[(size_t)t * gate_ld + h]))) : 1.0f;
   }
   for (int n = warp; n < N; n += num_warps) {
     const T* wr = w + ((size_t)h * N + n) * K;
@@ -137,7 +170,12 @@ headwise_linear_kernel(const T* __restrict__ x, long long x_ld, int x_hs, const 
 #pragma unroll
       for (int r = 0; r < HL_TOKENS; ++r) {
         const int t = t0 + r;
-        if (t < num_tokens) out[(size_t)t * out_ld + (size_t)h * out_hs + n] = from_float<T>(acc[r] * g[r]);
+        if (t < num_tokens) {
+          float scale = g[r];
+          if (gate != nullptr && gate_each)
+            scale = 1.0f / (1.0f + expf(-to_float(gate[(size_t)t * gate_ld + (size_t)h * N + n])));
+          out[(size_t)t * out_ld + (size_t)h * out_hs + n] = from_float<T>(acc[r] * scale);
+        }
       }
     }
   }
@@ -207,7 +245,7 @@ __global__ void __launch_bounds__(MW * NW * 32)
 headwise_linear_mma_kernel(const __nv_bfloat16* __restrict__ x, long long x_ld, int x_hs,
                            const __nv_bfloat16* __restrict__ w, __nv_bfloat16* __restrict__ out, long long out_ld,
                            int out_hs, const __nv_bfloat16* __restrict__ gate, long long gate_ld, int num_tokens,
-                           int N, int K, int vec_x, int vec_w, int pair_store) {
+                           int N, int K, int vec_x, int vec_w, int pair_store, int gate_each) {
   extern __shared__ __align__(16) unsigned char ht_smem[];
   constexpr int TOKENS = MW * 16, PER_WARP = NC / NW;
   const int kp = (K + 15) / 16 * 16, pitch = kp + 8;  // +8 bf16: rows land in different banks
@@ -225,10 +263,13 @@ headwise_linear_mma_kernel(const __nv_bfloat16* __restrict__ x, long long x_ld, 
   const int r0 = (warp % MW) * 16 + g, r1 = r0 + 8;
   const int c0 = (warp / MW) * PER_WARP;  // first output of this warp within the block's range
   float gate0 = 1.f, gate1 = 1.f;
-  if (gate != nullptr) {
+  if (gate != nullptr && !gate_each) {
     if (r0 < t_here) gate0 = 1.0f / (1.0f + expf(-to_float(gate[(size_t)(t0 + r0) * gate_ld + h])));
     if (r1 < t_here) gate1 = 1.0f / (1.0f + expf(-to_float(gate[(size_t)(t0 + r1) * gate_ld + h])));
   }
+  // One logit per output: the row's gate columns of this head, read where the output is stored.
+  const __nv_bfloat16* gate_r0 = gate_each && gate != nullptr ? gate + (size_t)(t0 + r0) * gate_ld + (size_t)h * N + n0 : nullptr;
+  const __nv_bfloat16* gate_r1 = gate_each && gate != nullptr ? gate + (size_t)(t0 + r1) * gate_ld + (size_t)h * N + n0 : nullptr;
   __syncthreads();
   float acc[PER_WARP / 8][4];
 #pragma unroll
@@ -252,6 +293,16 @@ headwise_linear_mma_kernel(const __nv_bfloat16* __restrict__ x, long long x_ld, 
   for (int j = 0; j < PER_WARP / 8; ++j) {
     if (j < tiles) {
       const int n = c0 + j * 8 + 2 * q;
+      if (gate_r0 != nullptr) {
+        if (r0 < t_here) {
+          if (n < n_here) acc[j][0] *= 1.0f / (1.0f + expf(-to_float(gate_r0[n])));
+          if (n + 1 < n_here) acc[j][1] *= 1.0f / (1.0f + expf(-to_float(gate_r0[n + 1])));
+        }
+        if (r1 < t_here) {
+          if (n < n_here) acc[j][2] *= 1.0f / (1.0f + expf(-to_float(gate_r1[n])));
+          if (n + 1 < n_here) acc[j][3] *= 1.0f / (1.0f + expf(-to_float(gate_r1[n + 1])));
+        }
+      }
       // Two neighbouring outputs as one 4-byte store where every row starts on an even element.
       if (r0 < t_here) {
         __nv_bfloat16* dst = out + (size_t)(t0 + r0) * out_ld + (size_t)h * out_hs + n0 + n;
@@ -278,7 +329,7 @@ headwise_linear_mma_kernel(const __nv_bfloat16* __restrict__ x, long long x_ld, 
 template <int MW, int NW, int NC>
 static int launch_headwise_mma(const void* x, long long x_ld, int x_hs, const void* w, void* out, long long out_ld,
                                int out_hs, const void* gate, long long gate_ld, int num_tokens, int H, int N, int K,
-                               cudaStream_t stream) {
+                               int gate_each, cudaStream_t stream) {
   const int pitch = (K + 15) / 16 * 16 + 8;
   const size_t bytes = sizeof(__nv_bfloat16) * (size_t)(MW * 16 + NC) * pitch;
   if (bytes > 48 * 1024)
@@ -288,7 +339,8 @@ static int launch_headwise_mma(const void* x, long long x_ld, int x_hs, const vo
   const int pair_store = (out_ld % 2) == 0 && (out_hs % 2) == 0 && (reinterpret_cast<uintptr_t>(out) & 3) == 0;
   launch_pdl(headwise_linear_mma_kernel<MW, NW, NC>, dim3((num_tokens + MW * 16 - 1) / (MW * 16), H, (N + NC - 1) / NC),
              dim3(MW * NW * 32), bytes, stream, (const __nv_bfloat16*)x, x_ld, x_hs, (const __nv_bfloat16*)w,
-             (__nv_bfloat16*)out, out_ld, out_hs, (const __nv_bfloat16*)gate, gate_ld, num_tokens, N, K, vec_x, vec_w, pair_store);
+             (__nv_bfloat16*)out, out_ld, out_hs, (const __nv_bfloat16*)gate, gate_ld, num_tokens, N, K, vec_x, vec_w, pair_store,
+             gate_each);
   return (int)cudaGetLastError();
 }
 
@@ -296,29 +348,45 @@ static int launch_headwise_mma(const void* x, long long x_ld, int x_hs, const vo
 
 using namespace vx;
 
-VX_API int vx_latent_prepare(const void* proj, long long proj_ld, int q_off, int dkv_off, int dtype,
+VX_API int vx_latent_prepare(const void* proj, long long proj_ld, const void* q_src, long long q_ld, int q_off,
+                             int dkv_off, int dtype,
                              const int* positions, const float* cos_t, const float* sin_t, int max_pos,
                              int rot_pairs, const float* latent_w, float eps, const int* slots, void* cache,
                              long long num_slots, void* qa, int num_tokens, int H, int dim, int R, int kr, int Dp,
-                             int* status, cudaStream_t stream) {
+                             int half_layout, int* status, cudaStream_t stream) {
   if (num_tokens <= 0) return 0;
   if (H <= 0 || dim < 0 || R < 0 || kr <= 0 || Dp < kr + R || 2 * rot_pairs > R) return (int)cudaErrorInvalidValue;
   if (dkv_off >= 0 && (cache == nullptr || slots == nullptr || latent_w == nullptr)) return (int)cudaErrorInvalidValue;
   const int threads = 128;
   if (dtype == VX_DTYPE_F32)
     launch_pdl(latent_prepare_kernel<float>, dim3(num_tokens), dim3(threads), 0, stream, (const float*)proj, proj_ld,
-               q_off, dkv_off, positions, cos_t, sin_t, max_pos, rot_pairs, latent_w, eps, slots, (float*)cache,
-               num_slots, (float*)qa, H, dim, R, kr, Dp, status);
+               (const float*)q_src, q_ld, q_off, dkv_off, positions, cos_t, sin_t, max_pos, rot_pairs, latent_w, eps, slots, (float*)cache,
+               num_slots, (float*)qa, H, dim, R, kr, Dp, half_layout, status);
   else
     launch_pdl(latent_prepare_kernel<__nv_bfloat16>, dim3(num_tokens), dim3(threads), 0, stream,
-               (const __nv_bfloat16*)proj, proj_ld, q_off, dkv_off, positions, cos_t, sin_t, max_pos, rot_pairs,
-               latent_w, eps, slots, (__nv_bfloat16*)cache, num_slots, (__nv_bfloat16*)qa, H, dim, R, kr, Dp, status);
+               (const __nv_bfloat16*)proj, proj_ld, (const __nv_bfloat16*)q_src, q_ld, q_off, dkv_off, positions, cos_t, sin_t, max_pos, rot_pairs,
+               latent_w, eps, slots, (__nv_bfloat16*)cache, num_slots, (__nv_bfloat16*)qa, H, dim, R, kr, Dp,
+               half_layout, status);
+  return (int)cudaGetLastError();
+}
+
+VX_API int vx_rms_rows(const void* x, long long x_ld, int dtype, const float* w, float eps, int n, void* out,
+                       long long out_ld, int n_out, int num_tokens, cudaStream_t stream) {
+  if (num_tokens <= 0) return 0;
+  if (n <= 0 || n_out < n) return (int)cudaErrorInvalidValue;
+  const int threads = n_out >= 256 ? 256 : (n_out + 31) / 32 * 32;
+  if (dtype == VX_DTYPE_F32)
+    launch_pdl(rms_rows_kernel<float>, dim3(num_tokens), dim3(threads), 0, stream, (const float*)x, x_ld, w, eps, n,
+               (float*)out, out_ld, n_out);
+  else
+    launch_pdl(rms_rows_kernel<__nv_bfloat16>, dim3(num_tokens), dim3(threads), 0, stream, (const __nv_bfloat16*)x,
+               x_ld, w, eps, n, (__nv_bfloat16*)out, out_ld, n_out);
   return (int)cudaGetLastError();
 }
 
 VX_API int vx_headwise_linear(const void* x, long long x_ld, int x_hs, const void* w, void* out, long long out_ld,
                               int out_hs, const void* gate, long long gate_ld, int dtype, int num_tokens, int H,
-                              int N, int K, cudaStream_t stream) {
+                              int N, int K, int gate_each, cudaStream_t stream) {
   if (num_tokens <= 0 || H <= 0 || N <= 0) return 0;
   if (K <= 0) return (int)cudaErrorInvalidValue;
   if (dtype == VX_DTYPE_BF16 && K <= HT_MAX_K) {
@@ -326,8 +394,8 @@ VX_API int vx_headwise_linear(const void* x, long long x_ld, int x_hs, const voi
     // heads' weights are read by many blocks at once; many tokens: 64 tokens a block against 128
     // outputs.
     if (num_tokens <= 32)
-      return launch_headwise_mma<1, 4, 64>(x, x_ld, x_hs, w, out, out_ld, out_hs, gate, gate_ld, num_tokens, H, N, K, stream);
-    return launch_headwise_mma<4, 1, 128>(x, x_ld, x_hs, w, out, out_ld, out_hs, gate, gate_ld, num_tokens, H, N, K, stream);
+      return launch_headwise_mma<1, 4, 64>(x, x_ld, x_hs, w, out, out_ld, out_hs, gate, gate_ld, num_tokens, H, N, K, gate_each, stream);
+    return launch_headwise_mma<4, 1, 128>(x, x_ld, x_hs, w, out, out_ld, out_hs, gate, gate_ld, num_tokens, H, N, K, gate_each, stream);
   }
   const size_t smem = sizeof(float) * HL_TOKENS * (size_t)K;
   if (smem > 96 * 1024) return -1;
@@ -336,14 +404,14 @@ VX_API int vx_headwise_linear(const void* x, long long x_ld, int x_hs, const voi
     if (smem > 48 * 1024)
       cudaFuncSetAttribute(headwise_linear_kernel<float>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     launch_pdl(headwise_linear_kernel<float>, grid, dim3(256), smem, stream, (const float*)x, x_ld, x_hs,
-               (const float*)w, (float*)out, out_ld, out_hs, (const float*)gate, gate_ld, num_tokens, N, K);
+               (const float*)w, (float*)out, out_ld, out_hs, (const float*)gate, gate_ld, num_tokens, N, K, gate_each);
   } else {
     if (smem > 48 * 1024)
       cudaFuncSetAttribute(headwise_linear_kernel<__nv_bfloat16>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                            (int)smem);
     launch_pdl(headwise_linear_kernel<__nv_bfloat16>, grid, dim3(256), smem, stream, (const __nv_bfloat16*)x, x_ld,
                x_hs, (const __nv_bfloat16*)w, (__nv_bfloat16*)out, out_ld, out_hs, (const __nv_bfloat16*)gate,
-               gate_ld, num_tokens, N, K);
+               gate_ld, num_tokens, N, K, gate_each);
   }
   return (int)cudaGetLastError();
 }

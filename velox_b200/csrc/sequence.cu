@@ -12,7 +12,10 @@
 //                                 recurrence S <- a S + b, all in float32
 //   rglru_scan_kernel             the recurrence over a sequence's tokens, times the other branch
 //   ssd_scan_kernel               S <- exp(A dt) S + dt B x^T,  y = S^T C + D x  per head
-//   gated_group_norm_kernel       (y * silu(z)) normed in equal parts by their own RMS, times w
+//   delta_rule_scan_kernel        S <- diag(w) S - (a u)(u^T S) + k v^T,  o = S^T r  per head, with the
+//                                 decay w, the removal rate a and the unit key u made on the way in
+//   gated_group_norm_kernel       (y * silu(z)) normed in equal parts by their own RMS, times w; or
+//                                 y normed in equal parts, times w, times sigmoid(z)
 //   dual_norm_mean_kernel         (rms(a) wa + rms(b) wb) / 2, written or added to the stream
 //   act_rows_kernel               gelu (tanh form), squared relu, silu on strided columns
 //   residual_add_kernel, gated_rows_add_kernel
@@ -37,6 +40,7 @@ __device__ __forceinline__ float sq_act(float v, int kind) {
   if (kind == 1) return sq_silu(v);
   if (kind == 2) return sq_gelu_tanh(v);
   if (kind == 3) { const float r = fmaxf(v, 0.f); return r * r; }
+  if (kind == 4) return tanhf(v);
   return v;
 }
 
@@ -538,17 +542,158 @@ __global__ void ssd_combine_kernel(float* __restrict__ state, long long state_st
   }
 }
 
+// ---------------------------------------------------------------------------------------------
+// Generalized delta rule.  Per head, with key size Dk and value size Dv, the state S is Dk x Dv:
+//     w_t = exp(-decay * sigmoid(wl_t + w0)),   a_t = sigmoid(al_t + a_bias),
+//     u_t = k_t / sqrt(sum(k_t^2) + key_eps)
+//     S_t = diag(w_t) S_(t-1) - (a_t * u_t) (u_t^T S_(t-1)) + k_t v_t^T,     o_t = S_t^T r_t
+// Both middle terms read the old state.  A column of S (one value channel) never meets another
+// column, so a block takes CB columns of one head of one sequence; RL lanes share a column, each
+// with DR_KP rows of it in registers, and the two sums over the rows (u^T S and S^T r) meet by
+// shuffles.  The token's vectors over the key channels are made once per block for a tile of
+// tokens (decay, removal rate and unit key in float32) and read from shared memory by every
+// column.  The state is stored [head][column][row], so a thread's rows are contiguous.
+constexpr int DR_KP = 16;
+
+template <typename T>
+__global__ void delta_rule_scan_kernel(const T* __restrict__ r_in, const T* __restrict__ k_in, const T* __restrict__ v_in,
+                                       const T* __restrict__ a_in, long long in_stride, const T* __restrict__ w_in,
+                                       long long w_stride, const float* __restrict__ w0,
+                                       const float* __restrict__ a_bias, float decay, float key_eps,
+                                       float* __restrict__ state, long long state_stride, float* __restrict__ out,
+                                       long long out_stride, int Dk, int Dv, int RL, int CB, int TT,
+                                       const int* __restrict__ q_start, const int* __restrict__ q_len,
+                                       const int* __restrict__ seq_slots) {
+  extern __shared__ __align__(16) float dr_smem[];
+  allow_dependents();
+  const int seq = blockIdx.x, h = blockIdx.y, tile = blockIdx.z;
+  const int n = q_len[seq];
+  if (n <= 0) return;
+  const int t_first = q_start[seq];
+  const int KD = RL * DR_KP;  // key channels padded to the lanes' rows
+  float* s_w = dr_smem;             // [TT][KD] decay
+  float* s_au = s_w + TT * KD;      // [TT][KD] removal rate times unit key
+  float* s_u = s_au + TT * KD;      // [TT][KD] unit key
+  float* s_k = s_u + TT * KD;       // [TT][KD] key
+  float* s_r = s_k + TT * KD;       // [TT][KD] receptance
+  float* s_v = s_r + TT * KD;       // [TT][CB] this block's value channels
+  const int p = threadIdx.x % RL, c = threadIdx.x / RL;
+  const int col = tile * CB + c;
+  const bool live = col < Dv;
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, num_warps = blockDim.x >> 5;
+  float* mine = state + (size_t)seq_slots[seq] * state_stride + ((size_t)h * Dv + (live ? col : 0)) * Dk;
+  float S[DR_KP];
+  grid_dependency_wait();
+#pragma unroll
+  for (int q = 0; q < DR_KP; ++q) {
+    const int row = p * DR_KP + q;
+    S[q] = (live && row < Dk) ? mine[row] : 0.f;
+  }
+  const size_t hk = (size_t)h * Dk;
+  for (int t0 = 0; t0 < n; t0 += TT) {
+    const int tt = min(TT, n - t0);
+    __syncthreads();
+    for (int idx = threadIdx.x; idx < tt * KD; idx += blockDim.x) {
+      const int i = idx / KD, ch = idx - i * KD;
+      float wv = 0.f, av = 0.f, kv = 0.f, rv = 0.f;
+      if (ch < Dk) {
+        const size_t at = (size_t)(t_first + t0 + i) * in_stride + hk + ch;
+        kv = to_float(k_in[at]);
+        rv = to_float(r_in[at]);
+        av = sq_sigmoid(to_float(a_in[at]) + a_bias[hk + ch]);
+        wv = expf(-decay * sq_sigmoid(to_float(w_in[(size_t)(t_first + t0 + i) * w_stride + hk + ch]) + w0[hk + ch]));
+      }
+      s_w[idx] = wv;
+      s_au[idx] = av;
+      s_k[idx] = kv;
+      s_r[idx] = rv;
+    }
+    for (int idx = threadIdx.x; idx < tt * CB; idx += blockDim.x) {
+      const int i = idx / CB, cc = idx - i * CB;
+      const int vc = tile * CB + cc;
+      s_v[idx] = vc < Dv ? to_float(v_in[(size_t)(t_first + t0 + i) * in_stride + (size_t)h * Dv + vc]) : 0.f;
+    }
+    __syncthreads();
+    // Unit keys: a warp per token, the sum over the key channels in a fixed order.
+    for (int i = warp; i < tt; i += num_warps) {
+      float ss = 0.f;
+      for (int ch = lane; ch < KD; ch += 32) ss = fmaf(s_k[i * KD + ch], s_k[i * KD + ch], ss);
+      ss = warp_sum(ss);
+      const float inv = 1.0f / sqrtf(ss + key_eps);
+      for (int ch = lane; ch < KD; ch += 32) {
+        const float u = s_k[i * KD + ch] * inv;
+        s_u[i * KD + ch] = u;
+        s_au[i * KD + ch] *= u;
+      }
+    }
+    __syncthreads();
+    for (int i = 0; i < tt; ++i) {
+      const float4* u4 = reinterpret_cast<const float4*>(s_u + i * KD + p * DR_KP);
+      const float4* w4 = reinterpret_cast<const float4*>(s_w + i * KD + p * DR_KP);
+      const float4* a4 = reinterpret_cast<const float4*>(s_au + i * KD + p * DR_KP);
+      const float4* k4 = reinterpret_cast<const float4*>(s_k + i * KD + p * DR_KP);
+      const float4* r4 = reinterpret_cast<const float4*>(s_r + i * KD + p * DR_KP);
+      float us = 0.f;
+#pragma unroll
+      for (int q = 0; q < DR_KP / 4; ++q) {
+        const float4 u = u4[q];
+        us = fmaf(u.x, S[4 * q], us);
+        us = fmaf(u.y, S[4 * q + 1], us);
+        us = fmaf(u.z, S[4 * q + 2], us);
+        us = fmaf(u.w, S[4 * q + 3], us);
+      }
+      for (int off = RL >> 1; off > 0; off >>= 1) us += __shfl_xor_sync(0xffffffffu, us, off);
+      const float vj = s_v[i * CB + c];
+      float o = 0.f;
+#pragma unroll
+      for (int q = 0; q < DR_KP / 4; ++q) {
+        const float4 w = w4[q], a = a4[q], k = k4[q], r = r4[q];
+        S[4 * q] = fmaf(w.x, S[4 * q], fmaf(-a.x, us, k.x * vj));
+        S[4 * q + 1] = fmaf(w.y, S[4 * q + 1], fmaf(-a.y, us, k.y * vj));
+        S[4 * q + 2] = fmaf(w.z, S[4 * q + 2], fmaf(-a.z, us, k.z * vj));
+        S[4 * q + 3] = fmaf(w.w, S[4 * q + 3], fmaf(-a.w, us, k.w * vj));
+        o = fmaf(S[4 * q], r.x, o);
+        o = fmaf(S[4 * q + 1], r.y, o);
+        o = fmaf(S[4 * q + 2], r.z, o);
+        o = fmaf(S[4 * q + 3], r.w, o);
+      }
+      for (int off = RL >> 1; off > 0; off >>= 1) o += __shfl_xor_sync(0xffffffffu, o, off);
+      if (live && p == 0) out[(size_t)(t_first + t0 + i) * out_stride + (size_t)h * Dv + col] = o;
+    }
+  }
+  if (live) {
+#pragma unroll
+    for (int q = 0; q < DR_KP; ++q) {
+      const int row = p * DR_KP + q;
+      if (row < Dk) mine[row] = S[q];
+    }
+  }
+}
+
 // out[t, part] = (y * silu(z)) / rms over the part * w, parts of equal size.
 template <typename T>
 __global__ void gated_group_norm_kernel(const float* __restrict__ y, long long y_stride, const T* __restrict__ z,
                                         long long z_stride, const float* __restrict__ w, float eps, int part,
-                                        T* __restrict__ out, long long out_stride) {
+                                        T* __restrict__ out, long long out_stride, int gate_after) {
   __shared__ float scratch[32];
   allow_dependents();
   grid_dependency_wait();
   const int t = blockIdx.x, gidx = blockIdx.y;
   const size_t off = (size_t)gidx * part;
   float ss = 0.f;
+  if (gate_after) {
+    // The part is normed as it is; weight and sigmoid(z) come after.
+    for (int i = threadIdx.x; i < part; i += blockDim.x) {
+      const float v = y[(size_t)t * y_stride + off + i];
+      ss = fmaf(v, v, ss);
+    }
+    const float inv = rsqrtf(block_sum(ss, scratch) / (float)part + eps);
+    for (int i = threadIdx.x; i < part; i += blockDim.x) {
+      const float v = y[(size_t)t * y_stride + off + i] * inv * w[off + i];
+      out[(size_t)t * out_stride + off + i] = from_float<T>(v * sq_sigmoid(to_float(z[(size_t)t * z_stride + off + i])));
+    }
+    return;
+  }
   for (int i = threadIdx.x; i < part; i += blockDim.x) {
     const float v = y[(size_t)t * y_stride + off + i] * sq_silu(to_float(z[(size_t)t * z_stride + off + i]));
     ss = fmaf(v, v, ss);
@@ -846,14 +991,46 @@ VX_API int vx_ssd_scan(const float* xbc, long long xbc_stride, const void* dt_in
 #undef VX_SSD
 }
 
+static int dr_pow2_at_least(int v) {
+  int p = 1;
+  while (p < v) p <<= 1;
+  return p;
+}
+
+VX_API int vx_delta_rule_scan(const void* r, const void* k, const void* v, const void* a, int dtype, long long in_stride,
+                              const void* w, long long w_stride, const float* w0, const float* a_bias, float decay,
+                              float key_eps, float* state, long long state_stride, float* out, long long out_stride,
+                              int heads, int Dk, int Dv, const int* q_start, const int* q_len, const int* seq_slots,
+                              int num_seqs, cudaStream_t stream) {
+  if (num_seqs <= 0) return 0;
+  if (heads <= 0 || Dk <= 0 || Dv <= 0) return (int)cudaErrorInvalidValue;
+  const int RL = dr_pow2_at_least((Dk + DR_KP - 1) / DR_KP);
+  if (RL > 32) return -1;
+  // Columns a block: 32 where the lanes allow, a whole number of warps at least.
+  int CB = 256 / RL;
+  if (CB > 32) CB = 32;
+  const int KD = RL * DR_KP;
+  const int TT = KD <= 64 ? 16 : (KD <= 128 ? 8 : 4);
+  const size_t smem = sizeof(float) * ((size_t)5 * TT * KD + (size_t)TT * CB);
+  const dim3 grid(num_seqs, heads, (Dv + CB - 1) / CB);
+  VX_BY_DTYPE(dtype, {
+    if (smem > 48 * 1024)
+      cudaFuncSetAttribute(delta_rule_scan_kernel<T>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    launch_pdl(delta_rule_scan_kernel<T>, grid, dim3(CB * RL), smem, stream, (const T*)r, (const T*)k, (const T*)v,
+               (const T*)a, in_stride, (const T*)w, w_stride, w0, a_bias, decay, key_eps, state, state_stride, out,
+               out_stride, Dk, Dv, RL, CB, TT, q_start, q_len, seq_slots);
+  });
+  return (int)cudaGetLastError();
+}
+
 VX_API int vx_gated_group_norm(const float* y, long long y_stride, const void* z, int dtype, long long z_stride,
                                const float* w, float eps, int inner, int parts, void* out, long long out_stride,
-                               int num_tokens, cudaStream_t stream) {
+                               int num_tokens, int gate_after, cudaStream_t stream) {
   if (num_tokens <= 0) return 0;
   const int part = inner / parts;
   const int threads = part >= 256 ? 256 : (part + 31) / 32 * 32;
   VX_BY_DTYPE(dtype, launch_pdl(gated_group_norm_kernel<T>, dim3(num_tokens, parts), dim3(threads), 0, stream, y,
-                                y_stride, (const T*)z, z_stride, w, eps, part, (T*)out, out_stride));
+                                y_stride, (const T*)z, z_stride, w, eps, part, (T*)out, out_stride, gate_after));
   return (int)cudaGetLastError();
 }
 

@@ -54,8 +54,12 @@ def load_model(model_dir: str, dtype: torch.dtype, device: torch.device, max_pos
     raw = read_config_json(model_dir)
     arch = architecture_of(raw)
     config = arch.parse_config(raw)
-    spec = arch.build_spec(config)
-    store = WeightStore(Checkpoint(model_dir), spec, dtype, device)
+    checkpoint = Checkpoint(model_dir)
+    sizes = {}
+    if arch.checkpoint_sizes is not None:
+        sizes = arch.checkpoint_sizes(config, lambda name: checkpoint.shape(name) if name in checkpoint else None)
+    spec = arch.build_spec(config, **sizes)
+    store = WeightStore(checkpoint, spec, dtype, device)
     model = CausalLM(spec, store, dtype, device, max_position=max_position)
     return config, spec, model
 

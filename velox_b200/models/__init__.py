@@ -1,2 +1,2 @@
 """Built-in architectures.  Importing this package registers them."""
-from . import lizizen, peratar, qwen2, redalix  # noqa: F401
+from . import lizizen, mamivik, peratar, qwen2, redalix  # noqa: F401

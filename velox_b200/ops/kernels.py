@@ -74,7 +74,7 @@ def core():
             _ptr, _ptr, _ptr, _ptr, _c_int, _c_int, _c_int, _c_int, _c_int, _c_ll, _c_int, _ptr, _ptr,
         ]
         lib.vx_gemm_bf16_glu.argtypes = [
-            _ptr, _ptr, _ptr, _ptr, _c_int, _c_int, _c_int, _c_int, _c_ll, _c_f, _c_f, _c_f, _ptr, _ptr,
+            _ptr, _ptr, _ptr, _ptr, _c_int, _c_int, _c_int, _c_int, _c_ll, _c_f, _c_f, _c_f, _c_f, _ptr, _ptr,
         ]
         lib.vx_gemm_bf16_xielu.argtypes = [
             _ptr, _ptr, _ptr, _ptr, _ptr, _c_int, _c_int, _c_int, _c_int, _c_ll, _c_ll, _c_int, _c_f, _c_f, _c_int,
@@ -94,12 +94,14 @@ def core():
         lib.vx_xielu.argtypes = [_ptr, _c_ll, _ptr, _c_int, _c_int, _c_int, _c_f, _c_f, _ptr]
         lib.vx_softcap.argtypes = [_ptr, _c_ll, _c_f, _ptr]
         lib.vx_cast_f32_to_bf16.argtypes = [_ptr, _ptr, _c_ll, _ptr]
+        lib.vx_rms_rows.argtypes = [_ptr, _c_ll, _c_int, _ptr, _c_f, _c_int, _ptr, _c_ll, _c_int, _c_int, _ptr]
         lib.vx_latent_prepare.argtypes = [
-            _ptr, _c_ll, _c_int, _c_int, _c_int, _ptr, _ptr, _ptr, _c_int, _c_int, _ptr, _c_f, _ptr, _ptr, _c_ll,
-            _ptr, _c_int, _c_int, _c_int, _c_int, _c_int, _c_int, _ptr, _ptr,
+            _ptr, _c_ll, _ptr, _c_ll, _c_int, _c_int, _c_int, _ptr, _ptr, _ptr, _c_int, _c_int, _ptr, _c_f, _ptr, _ptr, _c_ll,
+            _ptr, _c_int, _c_int, _c_int, _c_int, _c_int, _c_int, _c_int, _ptr, _ptr,
         ]
         lib.vx_headwise_linear.argtypes = [
-            _ptr, _c_ll, _c_int, _ptr, _ptr, _c_ll, _c_int, _ptr, _c_ll, _c_int, _c_int, _c_int, _c_int, _c_int, _ptr,
+            _ptr, _c_ll, _c_int, _ptr, _ptr, _c_ll, _c_int, _ptr, _c_ll, _c_int, _c_int, _c_int, _c_int, _c_int, _c_int,
+            _ptr,
         ]
         lib.vx_gemm_bf16_qkv_rope.argtypes = [
             _ptr, _c_int, _ptr, _c_ll, _ptr, _c_f, _ptr, _ptr, _ptr, _c_int, _c_int, _c_ll, _c_int,
@@ -141,7 +143,11 @@ def mixers():
         ]
         lib.vx_ssd_chunk_rows.restype = _c_int
         lib.vx_gated_group_norm.argtypes = [
-            _ptr, _c_ll, _ptr, _c_int, _c_ll, _ptr, _c_f, _c_int, _c_int, _ptr, _c_ll, _c_int, _ptr,
+            _ptr, _c_ll, _ptr, _c_int, _c_ll, _ptr, _c_f, _c_int, _c_int, _ptr, _c_ll, _c_int, _c_int, _ptr,
+        ]
+        lib.vx_delta_rule_scan.argtypes = [
+            _ptr, _ptr, _ptr, _ptr, _c_int, _c_ll, _ptr, _c_ll, _ptr, _ptr, _c_f, _c_f, _ptr, _c_ll, _ptr, _c_ll,
+            _c_int, _c_int, _c_int, _ptr, _ptr, _ptr, _c_int, _ptr,
         ]
         lib.vx_dual_norm_mean.argtypes = [_ptr, _ptr, _c_int, _ptr, _ptr, _c_f, _c_f, _c_int, _ptr, _ptr, _c_int, _ptr]
         lib.vx_act_rows.argtypes = [_ptr, _c_int, _c_ll, _ptr, _c_ll, _c_int, _c_int, _c_int, _ptr]
@@ -181,7 +187,11 @@ def heads():
             _ptr, _c_ll, _c_int, _c_f, _ptr, _ptr, _ptr, _ptr, _c_ll, _ptr, _ptr, _c_int, _ptr, _ptr, _ptr, _c_int,
             _c_int, _ptr,
         ]
-        lib.vx_add_rows.argtypes = [_ptr, _ptr, _ptr, _c_int, _c_ll, _ptr]
+        lib.vx_add_rows.argtypes = [_ptr, _ptr, _ptr, _c_int, _c_ll, _c_f, _c_f, _ptr]
+        lib.vx_norm_conv.argtypes = [
+            _ptr, _c_ll, _c_int, _c_f, _ptr, _ptr, _c_int, _ptr, _c_ll, _ptr, _c_int, _ptr, _ptr, _ptr, _c_int,
+            _c_int, _ptr,
+        ]
         lib.vx_diff_prepare.argtypes = [
             _ptr, _c_int, _c_ll, _ptr, _c_ll, _ptr, _ptr, _ptr, _ptr, _ptr, _c_f, _ptr, _ptr, _ptr, _c_int, _c_int,
             _c_int, _c_int, _c_int, _c_int, _c_int, _c_int, _c_ll, _c_int, _ptr, _ptr,
@@ -189,7 +199,7 @@ def heads():
         lib.vx_diff_combine.argtypes = [
             _ptr, _c_int, _c_ll, _ptr, _c_ll, _ptr, _c_ll, _c_int, _c_int, _c_int, _c_int, _c_f, _c_f, _c_f, _ptr,
         ]
-        lib.vx_clamped_glu.argtypes = [_ptr, _c_int, _c_ll, _ptr, _c_ll, _c_int, _c_int, _c_f, _c_f, _c_f, _ptr]
+        lib.vx_clamped_glu.argtypes = [_ptr, _c_int, _c_ll, _ptr, _c_ll, _c_int, _c_int, _c_f, _c_f, _c_f, _c_f, _ptr]
         _heads = lib
     return _heads
 
@@ -534,6 +544,8 @@ def latent_prepare(
     rot_dim: int,
     kv_rank: int,
     status: torch.Tensor,
+    half_layout: bool = False,
+    q_source: Optional[torch.Tensor] = None,
 ) -> None:
     """What a latent-attention layer does to its projections before attention (latent.cu).
 
@@ -542,13 +554,17 @@ def latent_prepare(
     (``rot_dim`` values) at ``latent_offset`` (None: the layer reads another layer's cache).
     ``queries`` [T, heads, D]: dims ``kv_rank ...`` get the rotated parts and zero padding.
     ``cache`` [pages, page, 1, D]: the token's row at ``slots[t]`` gets [rms-normed latent |
-    rotated key part | zeros]; a negative slot writes nothing."""
+    rotated key part | zeros]; a negative slot writes nothing.  ``half_layout``: dim i of a rotated
+    part is paired with dim i + pairs, not dims 2i and 2i + 1.  ``q_source`` [T, width']: the
+    queries come from this buffer (a projection of their own) at ``q_offset``, not from ``proj``."""
     dtype = proj.dtype
     _need(proj, dtype, "proj")
     _need(queries, dtype, "queries")
     _need(positions, torch.int32, "positions")
     _need(cos, torch.float32, "cos")
     _need(sin, torch.float32, "sin")
+    if q_source is not None:
+        _need(q_source, dtype, "q_source")
     padded = queries.shape[-1]
     if queries.numel() < num_tokens * num_heads * padded or proj.shape[0] < num_tokens:
         raise ValueError("latent_prepare: buffers do not hold the tokens")
@@ -562,13 +578,25 @@ def latent_prepare(
             raise ValueError("latent_prepare: cache rows or norm weight do not match the sizes")
         num_slots = cache.shape[0] * cache.shape[1]
     _check(
-        core().vx_latent_prepare(_p(proj), proj.stride(0), int(q_offset), int(latent_offset) if write else -1,
+        core().vx_latent_prepare(_p(proj), proj.stride(0), _p(q_source),
+                                 0 if q_source is None else q_source.stride(0), int(q_offset), int(latent_offset) if write else -1,
                                  _code(dtype), _p(positions), _p(cos), _p(sin), cos.shape[0], cos.shape[1],
                                  _p(latent_weight) if write else None, float(eps), _p(slots) if write else None,
                                  _p(cache) if write else None, num_slots, _p(queries), num_tokens, num_heads, dim,
-                                 rot_dim, kv_rank, padded, _p(status), _stream()),
+                                 rot_dim, kv_rank, padded, 1 if half_layout else 0, _p(status), _stream()),
         "latent_prepare",
     )
+
+
+def rms_rows(x: torch.Tensor, weight: torch.Tensor, eps: float, out: torch.Tensor, num_tokens: int) -> None:
+    """out[t, i] = x[t, i] / sqrt(mean(x[t]^2) + eps) * weight[i]; ``x`` may be a column range of a wider
+    buffer; columns of ``out`` beyond the width of ``x`` are set to zero."""
+    _need(weight, torch.float32, "weight")
+    n = x.shape[1]
+    if weight.numel() != n or out.dtype != x.dtype or out.shape[1] < n:
+        raise ValueError("rms_rows: widths do not agree")
+    _check(core().vx_rms_rows(_p(x), _pitched(x, "x"), _code(x.dtype), _p(weight), float(eps), n, _p(out),
+                              _pitched(out, "out"), out.shape[1], num_tokens, _stream()), "rms_rows")
 
 
 def headwise_linear(
@@ -582,9 +610,11 @@ def headwise_linear(
     num_tokens: int,
     gate: Optional[torch.Tensor] = None,
     gate_offset: int = 0,
+    gate_each: bool = False,
 ) -> None:
     """out[t, out_offset + h * out_head_stride + n] = sum_k weight[h, n, k] * x[t, x_offset + h *
-    x_head_stride + k], times sigmoid(gate[t, gate_offset + h]) with a gate.  ``x``, ``out`` and
+    x_head_stride + k], times sigmoid(gate[t, gate_offset + h]) with a gate, or, with ``gate_each``,
+    times sigmoid(gate[t, gate_offset + h * N + n]): a logit per output.  ``x``, ``out`` and
     ``gate`` are dense 2-D buffers in the dtype of ``weight`` [heads, N, K]; float32 sums."""
     dtype = weight.dtype
     _need(weight, dtype, "weight")
@@ -598,13 +628,13 @@ def headwise_linear(
     gate_ptr, gate_ld = None, 0
     if gate is not None:
         _need(gate, dtype, "gate")
-        if gate_offset + heads > gate.shape[1]:
+        if gate_offset + heads * (n if gate_each else 1) > gate.shape[1]:
             raise ValueError("headwise_linear: the gate columns do not fit the rows")
         gate_ptr, gate_ld = gate.data_ptr() + gate_offset * gate.element_size(), gate.stride(0)
     code = core().vx_headwise_linear(x.data_ptr() + x_offset * x.element_size(), x.stride(0), x_head_stride,
                                      _p(weight), out.data_ptr() + out_offset * out.element_size(), out.stride(0),
                                      out_head_stride, gate_ptr, gate_ld, _code(dtype), num_tokens, heads, n, k,
-                                     _stream())
+                                     1 if gate_each else 0, _stream())
     if code == -1:
         raise KernelError(f"headwise_linear refuses an inner size of {k}")
     _check(code, "headwise_linear")
@@ -736,8 +766,8 @@ def gemm_bf16(
 
 
 def gemm_bf16_glu(x: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor], out: torch.Tensor, num_rows: int,
-                  limit: float, alpha: float, up_shift: float, status: torch.Tensor) -> None:
-    """out[:num_rows] = g * sigmoid(alpha * g) * (u + up_shift) with g and u the two halves of
+                  limit: float, alpha: float, up_shift: float, status: torch.Tensor, cubic: float = 0.0) -> None:
+    """out[:num_rows] = g * sigmoid(alpha * (g + cubic * g^3)) * (u + up_shift) with g and u the two halves of
     x[:num_rows] @ w.T + bias (w [2 F, K]: the F gate rows, then the F up rows; bias [2 F] float32
     or None), g cut at ``limit`` from above and u to +-``limit`` when ``limit`` > 0, in the
     epilogue of the tcgen05 kernel: the activations' inputs never leave the SM."""
@@ -752,7 +782,7 @@ def gemm_bf16_glu(x: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor]
         if bias.numel() != n:
             raise ValueError(f"bias of {bias.numel()} elements for {n} rows")
     code = core().vx_gemm_bf16_glu(_p(x), _p(w), _p(bias), _p(out), num_rows, x.shape[0], n // 2, k, out.stride(0),
-                                   float(limit), float(alpha), float(up_shift), _p(status), _stream())
+                                   float(limit), float(alpha), float(up_shift), float(cubic), _p(status), _stream())
     if code == -1:
         raise KernelError(f"gemm_bf16_glu refuses x {tuple(x.shape)} w {tuple(w.shape)}")
     _check(code, "gemm_bf16_glu")
@@ -1300,7 +1330,7 @@ def apply_penalties(
 # ------------------------------------------------------------------------------------------
 # Recurrent mixers, expert feed-forwards and the row-wise kernels around them (csrc/sequence.cu,
 # csrc/routed.cu).  Tensors may be column ranges of wider buffers: a row pitch is passed.
-ACT_NONE, ACT_SILU, ACT_GELU_TANH, ACT_RELU_SQUARED = 0, 1, 2, 3
+ACT_NONE, ACT_SILU, ACT_GELU_TANH, ACT_RELU_SQUARED, ACT_TANH = 0, 1, 2, 3, 4
 
 
 def _pitched(t: torch.Tensor, name: str) -> int:
@@ -1436,14 +1466,41 @@ def ssd_scan(xbc, dt, dt_bias, a_log, d_skip, state, y_out, heads, groups, state
     )
 
 
-def gated_group_norm(y, z, weight, eps, parts, out, num_tokens) -> None:
-    """out = (y * silu(z)) divided, in ``parts`` equal parts, by each part's RMS, times weight."""
+def gated_group_norm(y, z, weight, eps, parts, out, num_tokens, gate_after=False) -> None:
+    """out = (y * silu(z)) divided, in ``parts`` equal parts, by each part's RMS, times weight; with
+    ``gate_after``: y divided by each part's RMS, times weight, times sigmoid(z)."""
     inner = weight.numel()
     _check(
         mixers().vx_gated_group_norm(_p(y), _pitched(y, "y"), _p(z), _code(z.dtype), _pitched(z, "z"), _p(weight),
-                                     float(eps), inner, parts, _p(out), _pitched(out, "out"), num_tokens, _stream()),
+                                     float(eps), inner, parts, _p(out), _pitched(out, "out"), num_tokens,
+                                     1 if gate_after else 0, _stream()),
         "gated_group_norm",
     )
+
+
+def delta_rule_scan(r, k, v, a, w, w0, a_bias, decay, key_eps, state, out, heads, key_dim, value_dim, q_start, q_len,
+                    seq_slots, num_seqs) -> None:
+    """The generalized delta rule over each sequence's tokens (csrc/sequence.cu).  ``r``, ``k``,
+    ``v``, ``a`` are column ranges of one projection buffer [tokens, *] (heads x key_dim, value_dim for
+    v), ``w`` the decay's logits [tokens, heads * key_dim]; ``w0``, ``a_bias`` float32 [heads *
+    key_dim]; ``state`` float32, a row per state slot holding [heads, value_dim, key_dim]; ``out``
+    float32 [tokens, heads * value_dim]."""
+    stride = _pitched(r, "r")
+    if _pitched(k, "k") != stride or _pitched(v, "v") != stride or _pitched(a, "a") != stride:
+        raise ValueError("delta_rule_scan: r, k, v and a are columns of one buffer")
+    if w.dtype != r.dtype or out.dtype != torch.float32 or state.dtype != torch.float32:
+        raise TypeError("delta_rule_scan: logits in the compute dtype, state and out float32")
+    _need(w0, torch.float32, "w0")
+    _need(a_bias, torch.float32, "a_bias")
+    if state.shape[1] < heads * key_dim * value_dim or state.stride(1) != 1:
+        raise ValueError("delta_rule_scan: the state row is too small")
+    code = mixers().vx_delta_rule_scan(
+        _p(r), _p(k), _p(v), _p(a), _code(r.dtype), stride, _p(w), _pitched(w, "w"), _p(w0), _p(a_bias),
+        float(decay), float(key_eps), _p(state), state.stride(0), _p(out), _pitched(out, "out"), heads, key_dim,
+        value_dim, _p(q_start), _p(q_len), _p(seq_slots), num_seqs, _stream())
+    if code == -1:
+        raise KernelError(f"delta_rule_scan refuses a key size of {key_dim} (at most 512)")
+    _check(code, "delta_rule_scan")
 
 
 def dual_norm_mean(a, b, w_a, w_b, eps, scale, num_tokens, resid=None, out=None) -> None:
@@ -1644,14 +1701,39 @@ def norm_shift(resid, weight, eps, out, num_tokens, q_start, q_len, seq_slots, n
            "norm_shift")
 
 
-def add_rows(resid, a, b, num_tokens) -> None:
-    """resid[:num_tokens] += a (+ b), float32 sums; a and b in the compute dtype, same row width."""
+def add_rows(resid, a, b, num_tokens, scale_a: float = 1.0, scale_b: float = 1.0) -> None:
+    """resid[:num_tokens] += scale_a * a (+ scale_b * b), float32 sums; a and b in the compute dtype,
+    same row width."""
     _need(resid, torch.float32, "resid")
     _need(a, a.dtype, "a")
     if b is not None:
         _need(b, a.dtype, "b")
-    _check(heads().vx_add_rows(_p(resid), _p(a), _p(b), _code(a.dtype), num_tokens * resid.shape[1], _stream()),
+    _check(heads().vx_add_rows(_p(resid), _p(a), _p(b), _code(a.dtype), num_tokens * resid.shape[1],
+                               float(scale_a), float(scale_b), _stream()),
            "add_rows")
+
+
+def norm_conv(resid, weight, eps, conv_weight, state, out, num_tokens, q_start, q_len, seq_slots, num_seqs) -> None:
+    """``out = h + conv(h)`` with ``h = resid / rms(resid) * weight`` per row and ``conv(h)_t = sum_j
+    conv_weight[:, j] * h_(t - taps + 1 + j)`` over a request's own tokens (zeros before its first).
+    ``state`` float32, a row per state slot: the request's last taps - 1 values of h, oldest first;
+    read for a portion's first rows and then rewritten."""
+    _need(resid, torch.float32, "resid")
+    _need(weight, torch.float32, "weight")
+    _need(conv_weight, torch.float32, "conv_weight")
+    width = resid.shape[1]
+    taps = conv_weight.shape[1]
+    if conv_weight.shape[0] != width or out.shape[1] != width or not out.is_contiguous():
+        raise ValueError("norm_conv: widths do not agree")
+    if taps > 1 and (state is None or state.dtype != torch.float32 or state.stride(-1) != 1
+                     or state.shape[1] < (taps - 1) * width):
+        raise ValueError("norm_conv needs a float32 state row of (taps - 1) * width values per slot")
+    code = heads().vx_norm_conv(_p(resid), resid.stride(0), width, float(eps), _p(weight), _p(conv_weight), taps,
+                                _p(state), 0 if state is None else state.stride(0), _p(out), _code(out.dtype),
+                                _p(q_start), _p(q_len), _p(seq_slots), int(num_seqs), int(num_tokens), _stream())
+    if code == -1:
+        raise KernelError(f"norm_conv refuses {taps} taps (1 to 8)")
+    _check(code, "norm_conv")
 
 
 def diff_prepare(proj, qbuf, positions, cos, sin, q_norm, k_norm, eps, slots, k_cache, v_cache, num_tokens,
@@ -1684,9 +1766,9 @@ def diff_combine(attn, gate, out, num_tokens, num_heads, vdim, head_dim, lam, ou
         _stream()), "diff_combine")
 
 
-def clamped_glu(gate_up, out, num_tokens, inner, limit, alpha, up_shift) -> None:
-    """``out = g * sigmoid(alpha * g) * (u + up_shift)`` with ``g = min(gate, limit)``, ``u =
+def clamped_glu(gate_up, out, num_tokens, inner, limit, alpha, up_shift, cubic: float = 0.0) -> None:
+    """``out = g * sigmoid(alpha * (g + cubic * g^3)) * (u + up_shift)`` with ``g = min(gate, limit)``, ``u =
     clamp(up, -limit, limit)`` (no clamps when ``limit`` is 0); gate columns first in ``gate_up``."""
     _check(heads().vx_clamped_glu(_p(gate_up), _code(gate_up.dtype), _pitched(gate_up, "gate_up"), _p(out),
                                   out.stride(0), num_tokens, inner, float(limit or 0.0), float(alpha),
-                                  float(up_shift), _stream()), "clamped_glu")
+                                  float(up_shift), float(cubic), _stream()), "clamped_glu")

@@ -12,8 +12,9 @@ need not be multiples of 16 (``key_dim``, ``value_dim``: the projections are lai
 head padded with zeros to ``head_dim``, which is what the kernels see); a window that keeps the
 first ``keep_first`` keys; a learned sink per head in the softmax denominator (``sink``); a gate
 per head on the heads' outputs, ``sigmoid(W_g x)`` (``head_gate``: its rows ride along behind
-q | k | v in the one projection).  Such a part takes its matrices as ``q.weight``, ``k.weight``,
-``v.weight`` (and biases) instead of one ``qkv.weight``.
+q | k | v in the one projection); ``values_from_keys``: there is no value projection, a token's
+values are its keys as projected (bias included), before the rotation.  Such a part takes its
+matrices as ``q.weight``, ``k.weight``, ``v.weight`` (and biases) instead of one ``qkv.weight``.
 
 Changes to the scores, made inside the attention kernels: ``distance_bias`` (weights ``bias_r1``,
 ``bias_r2``, one number each per query head): ``r1 ln(1 + r2 (i - j))`` is taken off the score of
@@ -108,14 +109,19 @@ class Attention(Mixer):
             out[:, :size] = t
             return out.reshape(heads * D, *t.shape[2:])
 
+        from_keys = bool(params.get("values_from_keys", False))
+        if from_keys and vd != kd:
+            raise ValueError(f"values_from_keys: value_dim={vd} must equal key_dim={kd}")
+        # Values that are the unrotated keys: the key rows stand a second time where the value rows
+        # would, so the value columns of the projection are the keys before the rotation.
         pieces = [padded_heads(self.expect("q.weight", (H * kd, E)), H, kd),
-                  padded_heads(self.expect("k.weight", (G * kd, E)), G, kd),
-                  padded_heads(self.expect("v.weight", (G * vd, E)), G, vd)]
+                  padded_heads(self.expect("k.weight", (G * kd, E)), G, kd)]
+        pieces.append(pieces[1] if from_keys else padded_heads(self.expect("v.weight", (G * vd, E)), G, vd))
         bias = None
         if params.get("qkv_bias", False):
             bias = [padded_heads(self.expect("q.bias", (H * kd,)), H, kd),
-                    padded_heads(self.expect("k.bias", (G * kd,)), G, kd),
-                    padded_heads(self.expect("v.bias", (G * vd,)), G, vd)]
+                    padded_heads(self.expect("k.bias", (G * kd,)), G, kd)]
+            bias.append(bias[1] if from_keys else padded_heads(self.expect("v.bias", (G * vd,)), G, vd))
         if self.head_gate:
             pieces.append(self.expect("gate.weight", (H, E)))
             if bias is not None:

@@ -3,6 +3,12 @@
 ``pre_norm`` is the reference's decoder layer (src/decoder_layer.py:34-54):
 ``h = h + mixer(norm(h)); h = h + feed_forward(norm(h))``.  The adds are fused into the norm
 that follows them, so a block leaves its last product pending in ``hidden.delta``.
+
+``input_conv`` (block weight ``conv`` [width, taps]): the mixer does not read ``h_t = norm(x_t)``
+but ``h_t + sum_j conv[:, j] * h_(t - taps + 1 + j)``, a causal convolution per channel over the
+request's own tokens (zeros before its first).  The last ``taps - 1`` values of h of a request are
+a float32 state row of the block.  Norm and convolution are one kernel.  A layer may then have
+no feed-forward.
 """
 from __future__ import annotations
 
@@ -20,11 +26,33 @@ _FUSE_NORMS = os.environ.get("VELOX_B200_NO_NORM_FUSION") != "1"
 
 @register_part("block", "pre_norm")
 class PreNormBlock:
-    def __init__(self, mixer, feed_forward, norms, params=None) -> None:
+    def __init__(self, mixer, feed_forward, norms, params=None, weights=None, dtype=None, device=None) -> None:
+        params = dict(params or {})
         self.mixer = mixer
         self.feed_forward = feed_forward
         self.norm_mixer = norms["mixer"]
-        self.norm_feed_forward = norms["feed_forward"]
+        self.norm_feed_forward = norms.get("feed_forward")
+        if feed_forward is not None and self.norm_feed_forward is None:
+            raise ValueError("a pre_norm block with a feed-forward needs its norm")
+        self.conv = None
+        if params.get("input_conv", False):
+            if weights is None or "conv" not in weights:
+                raise ValueError("a block with input_conv needs the weight 'conv'")
+            self.conv = weights["conv"]
+            if self.conv.dim() != 2 or self.conv.shape[0] != self.norm_mixer.size or not 1 <= self.conv.shape[1] <= 8:
+                raise ValueError(f"the weight 'conv' has shape {tuple(self.conv.shape)}, expected "
+                                 f"({self.norm_mixer.size}, taps) with 1 to 8 taps")
+            if self.norm_mixer.center:
+                raise ValueError("input_conv goes with an RMS norm")
+            kernels.heads()
+
+    def state_needs(self):
+        """(taps - 1) rows of the model's width per request: the last inputs of the convolution."""
+        if self.conv is None or self.conv.shape[1] < 2:
+            return None
+        from .base import StateSpec
+
+        return StateSpec(((self.conv.shape[1] - 1) * self.norm_mixer.size,))
 
     def forward(self, hidden: HiddenState, ctx, cache) -> None:
         T = ctx.num_tokens
@@ -39,8 +67,21 @@ class PreNormBlock:
         wants = getattr(self.feed_forward, "wants_residual_mirror", None)
         if wants is not None and wants(T, ctx):
             ctx.residual_mirror = ws.get("block.residual_mirror", (ws.max_tokens, hidden.resid.shape[1]), torch.float32)
-        mixed = self.mixer.forward(self._normed(self.norm_mixer, self.mixer, hidden.resid, hidden.delta, normed, T),
-                                   ctx, cache)
+        if self.conv is not None:
+            if hidden.delta is not None:
+                kernels.add_rows(hidden.resid, hidden.delta, None, T)
+            kernels.norm_conv(hidden.resid, self.norm_mixer.weight, self.norm_mixer.eps, self.conv,
+                              getattr(cache, "block_state", None), normed, T, ctx.q_start, ctx.q_len, ctx.seq_slots,
+                              ctx.num_seqs)
+            mixed = self.mixer.forward(normed, ctx, cache)
+        else:
+            mixed = self.mixer.forward(
+                self._normed(self.norm_mixer, self.mixer, hidden.resid, hidden.delta, normed, T), ctx, cache)
+        if self.feed_forward is None:
+            hidden.delta = mixed
+            ctx.residual = None
+            ctx.residual_mirror = None
+            return
         source = hidden.resid
         if mixed is None and ctx.residual_mirror is not None and ctx.residual_mirror_written:
             source = ctx.residual_mirror

@@ -20,6 +20,15 @@ named by the model's schedule (``cache.read_only``) with its own W_uk, W_uv and 
 
 ``side_rows`` > 0: the first rows of ``in.weight`` are not the mixer's; their products (plus
 ``side.bias``) belong to the block around it and are handed over as ``ctx.side_output``.
+
+Further forms, all chosen by parameters.  ``query_rank`` r > 0: the queries come through a latent
+of their own, ``q = W_uq rms_norm(W_dq x) * w``; ``in.weight`` then holds the r rows of W_dq where
+it otherwise holds W_q, and the part has ``uq.weight`` and ``query_norm.weight``.  ``window``: a
+query sees itself and the ``window - 1`` keys before it.  ``sink``: a learned number per head
+whose exponential joins the softmax denominator (weight ``sink``).  ``gate`` "element": the gate
+is ``sigmoid(W_g x)`` over all ``heads * value_dim`` outputs, not one number per head.  The
+position part decides which dims are a rotating pair (``layout``: neighbours, or dim i with dim
+i + pairs).
 """
 from __future__ import annotations
 
@@ -47,9 +56,15 @@ class LatentAttention(Mixer):
         self.eps = float(params["eps"])
         self.own_latent = bool(params.get("own_latent", True))
         self.gated = bool(params.get("output_gate", True))
+        self.gate_each = params.get("gate", "head") == "element"
+        if params.get("gate", "head") not in ("head", "element"):
+            raise ValueError(f"latent attention: gate is 'head' or 'element', not {params.get('gate')!r}")
         self.side_rows = int(params.get("side_rows", 0))
+        self.query_rank = int(params.get("query_rank") or 0)
+        self.window = params.get("window")
         if position is None or not hasattr(position, "pairs"):
             raise ValueError("latent attention needs a pair-rotating position encoding part")
+        self.half_layout = getattr(position, "layout", "pairs") == "half"
         if 2 * position.pairs > self.rot_dim:
             raise ValueError(f"the rotation covers {2 * position.pairs} dims, the rotated part has {self.rot_dim}")
         self.position = position
@@ -62,9 +77,10 @@ class LatentAttention(Mixer):
             )
         H, q_head = self.num_heads, self.dim + self.rot_dim
         self.q_offset = self.side_rows
-        self.latent_offset = self.q_offset + H * q_head
+        self.latent_offset = self.q_offset + (self.query_rank if self.query_rank else H * q_head)
         self.gate_offset = self.latent_offset + (self.kv_rank + self.rot_dim if self.own_latent else 0)
-        rows = self.gate_offset + (H if self.gated else 0)
+        self.gate_rows = (H * self.value_dim if self.gate_each else H) if self.gated else 0
+        rows = self.gate_offset + self.gate_rows
         self.w_in = self.expect("in.weight", (rows, self.hidden_size))
         # Rows of zeros up to a multiple of eight: the projection's output rows then start on
         # 16-byte boundaries in bfloat16, which the library GEMM of long steps and the vector
@@ -80,6 +96,17 @@ class LatentAttention(Mixer):
             if dtype != torch.float32:
                 self.b_in_lowp = self.b_in.to(dtype)
         self.latent_norm = self.expect("latent_norm.weight", (self.kv_rank,)) if self.own_latent else None
+        self.w_uq = self.query_norm = None
+        if self.query_rank:
+            # The normed query latent is padded with zeros to whole 16-byte rows; the matching
+            # columns of W_uq are zero.
+            self.query_norm = self.expect("query_norm.weight", (self.query_rank,))
+            w_uq = self.expect("uq.weight", (H * q_head, self.query_rank))
+            self.query_rank_padded = -(-self.query_rank // 8) * 8
+            if self.query_rank_padded != self.query_rank:
+                w_uq = torch.cat([w_uq, w_uq.new_zeros(H * q_head, self.query_rank_padded - self.query_rank)], dim=1)
+            self.w_uq = w_uq.contiguous()
+        self.sink = self.expect("sink", (H,)) if params.get("sink", False) else None
         # W_uk [H * dim, kv_rank] is used transposed per head (the contraction runs over dim).
         w_uk = self.expect("uk.weight", (H * self.dim, self.kv_rank))
         self.w_uk_t = w_uk.view(H, self.dim, self.kv_rank).transpose(1, 2).contiguous()
@@ -88,10 +115,12 @@ class LatentAttention(Mixer):
         kernels.attention_lib(self.row_dim)
 
     def cache_needs(self) -> CacheNeeds:
-        return CacheNeeds(paged=PagedCacheSpec(1, self.row_dim, None, values_in_keys=True))
+        return CacheNeeds(paged=PagedCacheSpec(1, self.row_dim, self.window, values_in_keys=True))
 
     def attention_signature(self):
-        return (1, self.num_heads, None, self.row_dim)
+        base = (1, self.num_heads, self.window, self.row_dim)
+        # A sink comes in where split key ranges are merged: such rows always take that way.
+        return base + (0, True) if self.sink is not None else base
 
     def forward(self, x, ctx, cache):
         T = ctx.num_tokens
@@ -107,19 +136,30 @@ class LatentAttention(Mixer):
 
         queries = ws.get(f"latent.queries{H * Dp}", (ws.max_tokens, H * Dp), self.dtype)
         group = ctx.groups[cache.group]
+        q_rows, q_offset = proj, self.q_offset
+        if self.query_rank:
+            # The queries' own latent: norm, then the second projection.
+            q_width = H * (self.dim + self.rot_dim)
+            latent_q = ws.get(f"latent.query_latent{self.query_rank_padded}", (ws.max_tokens, self.query_rank_padded),
+                              self.dtype)
+            kernels.rms_rows(proj[:, self.q_offset : self.q_offset + self.query_rank], self.query_norm, self.eps,
+                             latent_q, T)
+            q_rows, q_offset = ws.get(f"latent.q{q_width}", (ws.max_tokens, q_width), self.dtype), 0
+            linear(latent_q, self.w_uq, None, q_rows, T, status=ctx.status)
         kernels.latent_prepare(
-            proj, self.q_offset, self.latent_offset if self.own_latent else None, ctx.positions, self.position.cos,
+            proj, q_offset, self.latent_offset if self.own_latent else None, ctx.positions, self.position.cos,
             self.position.sin, self.latent_norm, self.eps, group.slot_mapping, cache.k,
             queries.view(ws.max_tokens, H, Dp), T, H, self.dim, self.rot_dim, self.kv_rank, ctx.status,
+            half_layout=self.half_layout, q_source=q_rows if self.query_rank else None,
         )
-        kernels.headwise_linear(proj, self.q_offset, self.dim + self.rot_dim, self.w_uk_t, queries, 0, Dp, T)
+        kernels.headwise_linear(q_rows, q_offset, self.dim + self.rot_dim, self.w_uk_t, queries, 0, Dp, T)
 
         attn = ws.get(f"latent.attn{H * Dp}", (ws.max_tokens, H * Dp), self.dtype)
         plan = ctx.attention_plan(cache.group, self.attention_signature())
         for kind, items, count in plan.launches:
             kernels.attention(
                 kind, queries, attn, cache.k, cache.k, group.block_tables, ctx.q_start, ctx.q_len,
-                ctx.kv_len, items, count, plan.partial_o, plan.partial_lse, H, 1, Dp, None,
+                ctx.kv_len, items, count, plan.partial_o, plan.partial_lse, H, 1, Dp, self.window,
                 self.softmax_scale, merge_items=plan.merge_items, split_counters=plan.split_counters,
                 status=ctx.status,
                 cluster=(plan.cluster if kind == kernels.ATTN_BF16_NARROW else
@@ -131,12 +171,13 @@ class LatentAttention(Mixer):
         if plan.num_merges and plan.split_counters is None:
             kernels.attention_merge(
                 attn, ctx.q_start, plan.merge_items, plan.num_merges, plan.partial_o, plan.partial_lse,
-                H, 1, Dp, max_rows=plan.merge_rows,
+                H, 1, Dp, max_rows=plan.merge_rows, sinks=self.sink,
             )
 
         heads_out = ws.get(f"latent.heads{H * self.value_dim}", (ws.max_tokens, H * self.value_dim), self.dtype)
         kernels.headwise_linear(attn, 0, Dp, self.w_uv, heads_out, 0, self.value_dim, T,
-                                gate=proj if self.gated else None, gate_offset=self.gate_offset)
+                                gate=proj if self.gated else None, gate_offset=self.gate_offset,
+                                gate_each=self.gate_each)
         out = ws.get("mixer.out", (ws.max_tokens, self.hidden_size), self.dtype)
         linear(heads_out, self.w_out, None, out, T, status=ctx.status)
         return out

@@ -214,10 +214,13 @@ class ClampedGLU(FeedForward):
     """A gated feed-forward with clamps and biases:
 
         g = min(W_g x + b_g, limit);   u = clamp(W_u x + b_u, -limit, limit)
-        y = g * sigmoid(alpha * g) * (u + up_shift);   out = W_d y + b_d
+        y = g * sigmoid(alpha * (g + cubic * g^3)) * (u + up_shift);   out = W_d y + b_d
 
     ``gate_up.weight`` holds the gate rows first, then the up rows (and ``gate_up.bias`` alike);
-    ``limit`` 0 means no clamps; ``alpha`` and ``up_shift`` default to 1 and 0, which is SwiGLU.
+    ``limit`` 0 means no clamps; ``alpha``, ``cubic`` and ``up_shift`` default to 1, 0 and 0, which is
+    SwiGLU; ``alpha`` = 2 sqrt(2 / pi) with ``cubic`` = 0.044715 is the tanh form of GELU on the gate,
+    ``g / 2 * (1 + tanh(sqrt(2 / pi) (g + 0.044715 g^3)))``, because ``(1 + tanh y) / 2 = sigmoid(2 y)``.
+    ``biases`` false: the part has no bias vectors.
     The activation is float32.  The inner width need not be a multiple of anything: both halves
     are padded with rows of zeros to a multiple of eight, which produce y = 0."""
 
@@ -230,6 +233,7 @@ class ClampedGLU(FeedForward):
         self.limit = float(params.get("limit") or 0.0)
         self.alpha = float(params.get("alpha", 1.0))
         self.up_shift = float(params.get("up_shift", 0.0))
+        self.cubic = float(params.get("cubic", 0.0))
         if self.limit < 0.0:
             raise ValueError(f"clamped_glu: limit={self.limit} must not be negative")
         w = self.expect("gate_up.weight", (2 * F, E))
@@ -255,11 +259,11 @@ class ClampedGLU(FeedForward):
         if ctx.status is not None and use_tensor_core_kernel(x, self.w_gate_up, T):
             # Few tokens: biases, clamps and activation in the projection's epilogue.
             kernels.gemm_bf16_glu(x, self.w_gate_up, self.b_gate_up, act, T, self.limit, self.alpha, self.up_shift,
-                                  ctx.status)
+                                  ctx.status, cubic=self.cubic)
         else:
             gate_up = ws.get(f"clamped_glu.gate_up{2 * Fp}", (ws.max_tokens, 2 * Fp), self.dtype)
             linear(x, self.w_gate_up, self.b_gate_up, gate_up, T, self.b_gate_up_lowp, status=ctx.status)
-            kernels.clamped_glu(gate_up, act, T, Fp, self.limit, self.alpha, self.up_shift)
+            kernels.clamped_glu(gate_up, act, T, Fp, self.limit, self.alpha, self.up_shift, cubic=self.cubic)
         if (ctx.residual is not None and ctx.status is not None and self.dtype != torch.float32
                 and use_tensor_core_kernel(act, self.w_down, T)):
             # Few tokens: the down projection (and its bias) goes straight into the float32 stream.

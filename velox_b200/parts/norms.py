@@ -13,13 +13,18 @@ from .registry import register_part
 class RMSNorm(Norm):
     """``out = v * rsqrt(mean(v^2) + eps) * weight`` with ``v = resid + delta``, in float32.
     ``weight_offset`` c: the stored weight lies around zero and the factor is ``c + weight``
-    (added once, in float32, when the part is built)."""
+    (added once, in float32, when the part is built).  ``scalar_weight``: the stored weight is one
+    number for all coordinates (a tensor without dimensions), spread over the row when the part
+    is built, so every kernel that takes a norm's weight vector takes this norm too."""
 
     def __init__(self, params, weights, dtype, device) -> None:
         super().__init__(params, weights, dtype, device)
         self.size = int(params["size"])
         self.eps = float(params["eps"])
-        self.weight = self.expect("weight", (self.size,))
+        if params.get("scalar_weight", False):
+            self.weight = self.expect("weight", ()).to(torch.float32).reshape(1).expand(self.size).contiguous()
+        else:
+            self.weight = self.expect("weight", (self.size,))
         offset = float(params.get("weight_offset", 0.0))
         if offset != 0.0:
             self.weight = (self.weight.to(torch.float32) + offset).contiguous()

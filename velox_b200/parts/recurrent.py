@@ -20,8 +20,18 @@ state S in one float32 row of the slot-indexed state array, which starts at zero
 takes its slot.  Gates, decays, step sizes and S are float32 whatever the compute dtype; the
 projections run in the compute dtype.
 
+``delta_rule``: the generalized delta rule.  ``heads`` heads of ``dim`` channels; one projection
+of the input gives ``r | k | v | g | a | w1`` (the last ``decay_rank`` rows are the first half of
+the decay's two small matrices).  In float32, per head and key channel, the decay is
+``w = exp(-decay_scale * sigmoid(W_w2 tanh(W_w1 x) + w0))`` and the removal rate ``a = sigmoid(W_a x
++ a_bias)``; with the unit key ``u = k / sqrt(sum(k^2) + key_eps)`` the state (``dim`` x ``dim`` per
+head, float32) goes ``S <- diag(w) S - (a * u)(u^T S) + k v^T``, both middle terms reading the old
+state, and the head's result is ``S^T r``, divided by its root mean square, times a weight over all
+heads' channels, times ``sigmoid(g)``, then W_o.
+
 ``side_by_side``: two mixers read the same input; the result is ``scale * (rms_norm(left) * w_l
-+ rms_norm(right) * w_r)`` over the model width.
++ rms_norm(right) * w_r)`` over the model width, or, with ``join`` = "weighted_sum",
+``left_scale * left + right_scale * right`` without norms.
 """
 from __future__ import annotations
 
@@ -33,7 +43,7 @@ from .base import CacheNeeds, Mixer, StateSpec
 from .registry import part_class, register_part
 
 _ACTS = {"none": kernels.ACT_NONE, "silu": kernels.ACT_SILU, "gelu_tanh": kernels.ACT_GELU_TANH,
-         "relu_squared": kernels.ACT_RELU_SQUARED}
+         "relu_squared": kernels.ACT_RELU_SQUARED, "tanh": kernels.ACT_TANH}
 
 
 def activation_code(name: str) -> int:
@@ -49,6 +59,15 @@ def _pad_rows(weight: torch.Tensor, multiple: int = 8) -> torch.Tensor:
     if width == rows:
         return weight
     return torch.cat([weight, weight.new_zeros((width - rows,) + tuple(weight.shape[1:]))]).contiguous()
+
+
+def _lowered_rows(sums: torch.Tensor, ws, dtype, num_rows: int) -> torch.Tensor:
+    """float32 rows in the compute dtype (for a block that has offered no stream to add into)."""
+    if dtype == torch.float32:
+        return sums
+    out = ws.get("side_by_side.out", (ws.max_tokens, sums.shape[1]), dtype)
+    kernels.cast_f32_to_bf16(sums, out, num_rows * sums.shape[1])
+    return out
 
 
 @register_part("mixer", "gated_linear_recurrence")
@@ -192,21 +211,93 @@ class StateSpace(Mixer):
         return out
 
 
+@register_part("mixer", "delta_rule")
+class DeltaRule(Mixer):
+    takes_padded_steps = True
+
+    def __init__(self, params, weights, dtype, device, position=None) -> None:
+        super().__init__(params, weights, dtype, device)
+        self.hidden_size = E = int(params["hidden_size"])
+        self.heads = H = int(params["heads"])
+        self.dim = D = int(params["dim"])
+        self.eps = float(params["eps"])
+        self.decay_scale = float(params["decay_scale"])
+        self.key_eps = float(params.get("key_eps", 1e-6))
+        self.decay_rank = R = int(params["decay_rank"])
+        if D > 512:
+            raise ValueError(f"dim={D} is more than the scan kernel holds in a column's lanes (512)")
+        self.inner = inner = H * D
+        # r | k | v | g | a | w1 in one projection.  W_w1 is followed by rows of zeros up to a
+        # multiple of eight, so tanh(W_w1 x) comes out padded with zeros to whole 16-byte rows; the
+        # matching columns of W_w2 are zero.
+        self.rank_padded = -(-R // 8) * 8
+        w_in = self.expect("in.weight", (5 * inner + R, E))
+        if self.rank_padded != R:
+            w_in = torch.cat([w_in, w_in.new_zeros(self.rank_padded - R, E)])
+        self.w_in = _pad_rows(w_in)
+        self.in_width = self.w_in.shape[0]
+        w2 = self.expect("decay_up.weight", (inner, R))
+        if self.rank_padded != R:
+            w2 = torch.cat([w2, w2.new_zeros(inner, self.rank_padded - R)], dim=1)
+        self.w_decay_up = w2.contiguous()
+        self.decay_bias = self.expect("decay_bias", (inner,))
+        self.removal_bias = self.expect("removal_bias", (inner,))
+        self.norm_w = self.expect("norm.weight", (inner,))
+        self.w_out = self.expect("out.weight", (E, inner))
+        self.state_elems = H * D * D
+        kernels.mixers()
+
+    def cache_needs(self) -> CacheNeeds:
+        return CacheNeeds(state=StateSpec(shape=(self.state_elems,), dtype=torch.float32))
+
+    def forward(self, x, ctx, cache):
+        T, inner = ctx.num_tokens, self.inner
+        ws = ctx.workspace
+        if hasattr(x, "materialize"):
+            x = x.materialize()
+        proj = ws.get(f"delta_rule.in{self.in_width}", (ws.max_tokens, self.in_width), self.dtype)
+        linear(x, self.w_in, None, proj, T, status=ctx.status)
+        # The decay's logits: the second small matrix on the tanh of the first one's product.
+        bent = ws.get(f"delta_rule.bent{self.rank_padded}", (ws.max_tokens, self.rank_padded), self.dtype)
+        kernels.act_rows(proj[:, 5 * inner : 5 * inner + self.rank_padded], bent, T, kernels.ACT_TANH)
+        logits = ws.get(f"delta_rule.decay{inner}", (ws.max_tokens, inner), self.dtype)
+        linear(bent, self.w_decay_up, None, logits, T, status=ctx.status)
+        y = ws.get(f"delta_rule.y{inner}", (ws.max_tokens, inner), torch.float32)
+        kernels.delta_rule_scan(
+            proj[:, :inner], proj[:, inner : 2 * inner], proj[:, 2 * inner : 3 * inner],
+            proj[:, 4 * inner : 5 * inner], logits, self.decay_bias, self.removal_bias, self.decay_scale,
+            self.key_eps, cache.state, y, self.heads, self.dim, self.dim, ctx.q_start, ctx.q_len, ctx.seq_slots,
+            ctx.num_seqs)
+        normed = ws.get(f"delta_rule.normed{inner}", (ws.max_tokens, inner), self.dtype)
+        kernels.gated_group_norm(y, proj[:, 3 * inner : 4 * inner], self.norm_w, self.eps, self.heads, normed, T,
+                                 gate_after=True)
+        out = ws.get(f"delta_rule.out{self.hidden_size}", (ws.max_tokens, self.hidden_size), self.dtype)
+        linear(normed, self.w_out, None, out, T, status=ctx.status)
+        return out
+
+
 @register_part("mixer", "side_by_side")
 class SideBySide(Mixer):
     """Two mixers on the same input.  ``params``: ``left`` and ``right``, each {kind, params};
     the weights of each child carry its prefix (``left.``, ``right.``); ``left.out_norm`` and
     ``right.out_norm`` are the weights of the RMS norms on the children's results; ``scale``
-    (0.5: half the sum), ``eps``.  The children's caches are this part's: pages from the one,
-    a state row from the other."""
+    (0.5: half the sum), ``eps``.  With ``join`` = "weighted_sum" there are no norms and the
+    result is ``left_scale * left + right_scale * right``, summed in float32.  The children's
+    caches are this part's: pages from the one, a state row from the other."""
 
     takes_padded_steps = True
 
     def __init__(self, params, weights, dtype, device, position=None) -> None:
         super().__init__(params, weights, dtype, device)
         self.hidden_size = int(params["hidden_size"])
-        self.eps = float(params["eps"])
+        self.join = params.get("join", "normed_mean")
+        if self.join not in ("normed_mean", "weighted_sum"):
+            raise ValueError(f"side_by_side: join is 'normed_mean' or 'weighted_sum', not {self.join!r}")
+        self.weighted = self.join == "weighted_sum"
+        self.eps = float(params.get("eps", 0.0))
         self.scale = float(params.get("scale", 0.5))
+        self.left_scale = float(params.get("left_scale", 1.0))
+        self.right_scale = float(params.get("right_scale", 1.0))
         self.children = []
         for side in ("left", "right"):
             child = params[side]
@@ -214,8 +305,12 @@ class SideBySide(Mixer):
                    if name.startswith(side + ".") and name != f"{side}.out_norm"}
             cls = part_class("mixer", child["kind"])
             self.children.append(cls(child["params"], own, dtype, device, position=position))
-        self.norm_left = self.expect("left.out_norm", (self.hidden_size,))
-        self.norm_right = self.expect("right.out_norm", (self.hidden_size,))
+        if self.weighted:
+            self.norm_left = self.norm_right = None
+            kernels.heads()
+        else:
+            self.norm_left = self.expect("left.out_norm", (self.hidden_size,))
+            self.norm_right = self.expect("right.out_norm", (self.hidden_size,))
         needs = [c.cache_needs() for c in self.children]
         if sum(n.paged is not None for n in needs) > 1 or sum(n.state is not None for n in needs) > 1:
             raise ValueError("side_by_side: at most one child may keep pages and at most one a state")
@@ -244,6 +339,14 @@ class SideBySide(Mixer):
         left = self.children[0].forward(x, ctx, cache)
         right = self.children[1].forward(x, ctx, cache)
         ctx.residual = stream
+        if self.weighted:
+            if stream is not None:
+                kernels.add_rows(stream, left, right, T, self.left_scale, self.right_scale)
+                return None
+            sums = ctx.workspace.get("side_by_side.sums", (ctx.workspace.max_tokens, self.hidden_size), torch.float32)
+            sums[:T].zero_()
+            kernels.add_rows(sums, left, right, T, self.left_scale, self.right_scale)
+            return _lowered_rows(sums, ctx.workspace, self.dtype, T)
         if stream is not None:
             kernels.dual_norm_mean(left, right, self.norm_left, self.norm_right, self.eps, self.scale, T,
                                    resid=stream)

@@ -15,8 +15,35 @@ from .base import PositionEncoding
 from .registry import register_part
 
 
+def stretch_slow_pairs(inv_freq: torch.Tensor, rotary_dim: int, base: float, scaling) -> tuple:
+    """YaRN: ``scaling`` = {factor, original, fast, slow}.  With ``turn(t) = rotary_dim *
+    ln(original / (2 pi t)) / (2 ln base)``, ``lo = max(floor(turn(fast)), 0)``, ``hi =
+    min(ceil(turn(slow)), rotary_dim - 1)`` and ``ramp_i = clamp((i - lo) / max(hi - lo, 0.001),
+    0, 1)``, pair i turns by ``f_i / factor * ramp_i + f_i * (1 - ramp_i)`` per position, and cos and
+    sin are multiplied by ``0.1 ln(factor) + 1``.  Returns (frequencies, that magnitude)."""
+    import math
+
+    factor, original = float(scaling["factor"]), float(scaling["original"])
+
+    def turn(turns: float) -> float:
+        return rotary_dim * math.log(original / (2.0 * math.pi * turns)) / (2.0 * math.log(base))
+
+    lo = max(math.floor(turn(float(scaling["fast"]))), 0)
+    hi = min(math.ceil(turn(float(scaling["slow"]))), rotary_dim - 1)
+    index = torch.arange(inv_freq.numel(), dtype=torch.float64)
+    ramp = ((index - lo) / max(hi - lo, 0.001)).clamp(0.0, 1.0)
+    inv_freq = inv_freq.to(torch.float64)
+    return inv_freq / factor * ramp + inv_freq * (1.0 - ramp), 0.1 * math.log(factor) + 1.0
+
+
 @register_part("position", "rotary_half")
 class RotaryHalf(PositionEncoding):
+    """``scaling`` = {factor, original, fast, slow} stretches the slow pairs (``stretch_slow_pairs``;
+    the angles are then formed in float64).  ``layout`` tells a mixer that rotates with its own
+    kernel which dims are a pair: dim i with dim i + rotary_dim / 2."""
+
+    layout = "half"
+
     def __init__(self, params, weights, dtype, device) -> None:
         super().__init__(params, weights, dtype, device)
         self.head_dim = int(params["head_dim"])
@@ -30,16 +57,24 @@ class RotaryHalf(PositionEncoding):
             )
         # ``angles``: "float32" forms position * frequency in float32 (the reference's tables);
         # "float64" forms it in float64 and rounds the cosine and sine once.
-        precise = params.get("angles", "float32") == "float64"
+        scaling = params.get("scaling")
+        precise = params.get("angles", "float32") == "float64" or bool(scaling)
         work = torch.float64 if precise else torch.float32
         exponent = torch.arange(0, self.rotary_dim, 2, dtype=work) / self.rotary_dim
         inv_freq = 1.0 / (self.theta ** exponent)
+        magnitude = 1.0
+        if scaling:
+            inv_freq, magnitude = stretch_slow_pairs(inv_freq, self.rotary_dim, self.theta, scaling)
         positions = torch.arange(self.max_position, dtype=work)
         if self.scaling_factor != 1.0:
             positions = positions / self.scaling_factor
         angles = torch.outer(positions, inv_freq)
-        self.cos = angles.cos().to(torch.float32).to(device).contiguous()
-        self.sin = angles.sin().to(torch.float32).to(device).contiguous()
+        cos, sin = angles.cos(), angles.sin()
+        if magnitude != 1.0:
+            cos, sin = cos * magnitude, sin * magnitude
+        self.pairs = self.rotary_dim // 2
+        self.cos = cos.to(torch.float32).to(device).contiguous()
+        self.sin = sin.to(torch.float32).to(device).contiguous()
 
     def rotate_and_store(self, qkv, ctx, slots, k_cache, v_cache, num_heads, num_kv_heads):
         kernels.rope_cache_write(
@@ -105,6 +140,8 @@ class RotaryInterleaved(PositionEncoding):
     lo, 0.001), 0, 1)``, pair i turns by ``f_i / factor * ramp_i + f_i * (1 - ramp_i)`` per
     position, and cos and sin are multiplied by ``0.1 ln(factor) + 1``."""
 
+    layout = "pairs"
+
     def __init__(self, params, weights, dtype, device) -> None:
         super().__init__(params, weights, dtype, device)
         self.rotary_dim = int(params["rotary_dim"])
@@ -119,18 +156,7 @@ class RotaryInterleaved(PositionEncoding):
         magnitude = 1.0
         scaling = params.get("scaling")
         if scaling:
-            import math
-
-            factor, original = float(scaling["factor"]), float(scaling["original"])
-
-            def turn(turns: float) -> float:
-                return self.rotary_dim * math.log(original / (2.0 * math.pi * turns)) / (2.0 * math.log(self.base))
-
-            lo = max(math.floor(turn(float(scaling["fast"]))), 0)
-            hi = min(math.ceil(turn(float(scaling["slow"]))), self.rotary_dim - 1)
-            ramp = ((torch.arange(pairs, dtype=torch.float64) - lo) / max(hi - lo, 0.001)).clamp(0.0, 1.0)
-            inv_freq = inv_freq / factor * ramp + inv_freq * (1.0 - ramp)
-            magnitude = 0.1 * math.log(factor) + 1.0
+            inv_freq, magnitude = stretch_slow_pairs(inv_freq, self.rotary_dim, self.base, scaling)
         angles = torch.outer(torch.arange(self.max_position, dtype=torch.float64), inv_freq)
         width = max(pairs, 1)
         cos = torch.ones((self.max_position, width), dtype=torch.float32)

@@ -37,6 +37,9 @@ class WeightSpec:
     @property
     def shape(self) -> Tuple[int, ...]:
         first = self.sources[0].shape
+        if len(first) == 0:
+            # One number (a norm's single weight): nothing to concatenate.
+            return ()
         rows = sum(src.shape[0] for src in self.sources)
         return (rows,) + tuple(first[1:])
 
