@@ -635,11 +635,11 @@ def _reference_numbers(args, ref_root):
 
 
 def run_compare(args):
-    """``--compare-designs SIZE,...``: one layer of the Peratar, Redalix and Lizizen designs
+    """``--compare-designs SIZE,...``: one layer of the Peratar, Redalix, Lizizen and Mamivik designs
     beside one layer of the Qwen2 design at the same width, head count and feed-forward weight
-    count per token (the presets ``peratar-<size>``, ``redalix-<size>``, ``lizizen-<size>`` and
+    count per token (the presets ``peratar-<size>``, ``redalix-<size>``, ``lizizen-<size>``, ``mamivik-<size>`` and
     ``<size>`` of ``velox_b200.config.presets``), random weights.  A Redalix "layer" is the mean
-    over one period of its pattern of four layers, a Lizizen "layer" the mean of its two kinds.  Per
+    over one period of its pattern of four layers, a Lizizen or Mamivik "layer" the mean of its two kinds.  Per
     design and size: the time of a decode layer (``--batch`` requests behind 4,096 keys) against
     its bytes and the measured copy bandwidth, the time of a 2,048-token prompt layer against its
     operations and the measured library bf16 rate, and the time a layer spends in every kind of
@@ -654,7 +654,7 @@ def run_compare(args):
     few, many = 2, 6
     rows = []
     for size in args.compare_designs.split(","):
-        for name in (size, "peratar-" + size, "redalix-" + size, "lizizen-" + size):
+        for name in (size, "peratar-" + size, "redalix-" + size, "lizizen-" + size, "mamivik-" + size):
             if args.designs and name.split("-")[0] not in args.designs.split(",") and not (
                     "-" not in name and "qwen2" in args.designs.split(",")):
                 continue
@@ -672,7 +672,8 @@ def run_compare(args):
             flops = roofline.layer_flops(cfg, PREFILL_TOKENS, 0)
             row = {
                 "design": ("Peratar" if name.startswith("peratar-") else "Redalix" if name.startswith("redalix-")
-                           else "Lizizen" if name.startswith("lizizen-") else "Qwen2"),
+                           else "Lizizen" if name.startswith("lizizen-")
+                           else "Mamivik" if name.startswith("mamivik-") else "Qwen2"),
                 "size": size,
                 "decode": {"batch": args.batch, "keys": keys, "us_per_layer": round(decode_s * 1e6, 1),
                            "layer_bytes": weights + cached, "us_by_bytes": round((weights + cached) / (peaks["hbm_gbs"] * 1e9) * 1e6, 1),
@@ -709,7 +710,7 @@ def main():
                         help="instead of the benchmark: one layer of the Peratar, Redalix and Lizizen designs beside one of the "
                              "Qwen2 design at the named sizes (0.5b, 1.5b, 3b), decode and prefill")
     parser.add_argument("--designs", default=None, metavar="NAME,...",
-                        help="with --compare-designs: only these designs (qwen2, peratar, redalix, lizizen)")
+                        help="with --compare-designs: only these designs (qwen2, peratar, redalix, lizizen, mamivik)")
     args = parser.parse_args()
     world = int(os.environ.get("WORLD_SIZE", "1"))
     if args.gpus > 1 or world > 1:

@@ -81,6 +81,9 @@ def test_named_model_sizes_are_configurations_of_the_architecture():
         if name.startswith("lizizen-") or name == "tiny-l":
             assert arch.name == "Lizizen" and len(typed.layers) == len(cfg["layers"])
             continue
+        if name.startswith("mamivik-") or name == "tiny-m":
+            assert arch.name == "Mamivik" and len(typed.layers) == len(cfg["layers"])
+            continue
         assert arch.name == "Qwen2ForCausalLM"
         c = Qwen2Config.from_dict(cfg)
         assert c.num_attention_heads % c.num_key_value_heads == 0

@@ -148,12 +148,64 @@ def _lizizen_layer(entry: Dict, width: int, tokens: int, batch: int, context: in
     return 2 * weights, cache, flops
 
 
+def _is_mamivik(config_json: Dict) -> bool:
+    return config_json.get("architecture") == "Mamivik" or "Mamivik" in (config_json.get("architectures") or [])
+
+
+def _mamivik_layer(entry: Dict, width: int, tokens: int, batch: int, context: int):
+    """(bytes of weights read, bytes of cache and state touched, operations) of one Mamivik layer
+    for ``tokens`` new tokens of each of ``batch`` sequences behind ``context`` keys.  A window
+    bounds the keys a token reads; the latent layer's scores and sums run over the cached rows, as
+    the engine computes them; the delta rule's state is read and written once a step and costs six
+    operations per entry and token; the decay's inner size is the random-weights default."""
+    from ..config.model_config import DeltaRuleConfig
+    from ..models.mamivik import default_decay_rank
+
+    m = entry["mixer"]
+    rows = batch * tokens
+    cache = batch * 3 * width * 4 * 2  # the convolution's rows (at most; read and written)
+    flops = 0.0
+
+    def pairs_within(reach):
+        if tokens <= 4096:
+            return sum(min(context + i + 1, reach) for i in range(tokens))
+        return tokens * min(reach, context + tokens / 2)
+
+    if entry["type"] == "latent_attention":
+        heads, q_head, row = m["heads"], m["dim"] + m["rot_dim"], m["kv_rank"] + m["rot_dim"]
+        padded = -(-row // 16) * 16
+        weights = ((m["q_rank"] + row + heads * m["vdim"]) * width + heads * q_head * m["q_rank"]
+                   + heads * (m["dim"] + m["vdim"]) * m["kv_rank"] + width * heads * m["vdim"])
+        reach = m["mask"]["size"]
+        cache += batch * min(context + tokens, reach + tokens) * padded * 2
+        flops += 2.0 * rows * weights + 4.0 * batch * pairs_within(reach) * heads * padded
+    else:
+        a, d = m["left"], m["right"]
+        head = -(-a["dim"] // 16) * 16
+        inner = d["heads"] * d["dim"]
+        rank = default_decay_rank(DeltaRuleConfig(d["heads"], d["dim"]))
+        weights = (width * (a["heads"] + a["kv_heads"]) * a["dim"] + a["heads"] * a["dim"] * width
+                   + (5 * inner + rank) * width + inner * rank + inner * width)
+        reach = a["mask"]["size"]
+        cache += batch * min(context + tokens, reach + tokens) * 2 * a["kv_heads"] * head * 2
+        cache += batch * inner * d["dim"] * 4 * 2
+        flops += 2.0 * rows * weights + 4.0 * batch * pairs_within(reach) * a["heads"] * head
+        flops += 6.0 * rows * inner * d["dim"]
+    mlp = entry.get("mlp")
+    if mlp is not None:
+        weights += 3 * mlp["ff"] * width
+        flops += 2.0 * rows * 3 * mlp["ff"] * width
+    return 2 * weights, cache, flops
+
+
 def _listed_layer(config_json: Dict):
     """The per-layer accounting of a design whose layers differ in kind, or None."""
     if _is_redalix(config_json):
         return _redalix_layer
     if _is_lizizen(config_json):
         return _lizizen_layer
+    if _is_mamivik(config_json):
+        return _mamivik_layer
     return None
 
 

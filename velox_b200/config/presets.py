@@ -1,5 +1,5 @@
-"""Named example configurations of the Qwen2.5 dense family, and of the Peratar, Redalix and Lizizen
-designs at the same widths, as ``config.json`` dictionaries.
+"""Named example configurations of the Qwen2.5 dense family, and of the Peratar, Redalix, Lizizen and
+Mamivik designs at the same widths, as ``config.json`` dictionaries.
 
 They exist for runs with random weights (``--model-size`` of the benchmark command line): no
 checkpoint is needed to time the layer sizes of a published model.  Nothing in the engine
@@ -165,7 +165,60 @@ def _lizizen_tiny() -> Dict[str, Any]:
             "loop": {"start": 0, "stop": 2, "times": 2}, "max_position_embeddings": 512}
 
 
+def _mamivik(like: str, rot_dim: int = 32, kv_rank: int = 96, window: int = 1024) -> Dict[str, Any]:
+    """A Mamivik configuration with the width, head counts, layer count, feed-forward width and
+    vocabulary of the named Qwen2.5 size.  Its layers alternate ``latent_attention`` (query heads as
+    wide as that model's, ``rot_dim`` of their dims rotating, values as wide as its heads, a
+    latent of ``kv_rank`` values, queries through a latent of a quarter of the width) and
+    ``parallel`` (left: that model's heads over a window; right: a delta rule of as many channels
+    as the left mixer has key channels, in heads of 64)."""
+    base = MODEL_SIZES[like]
+    width, heads, kv_heads = base["hidden_size"], base["num_attention_heads"], base["num_key_value_heads"]
+    head = base.get("head_dim") or width // heads
+    mlp = {"kind": "dense", "ff": base["intermediate_size"]}
+    latent = {"heads": heads, "dim": head - rot_dim, "rot_dim": rot_dim, "vdim": head, "kv_rank": kv_rank,
+              "q_rank": width // 4 // 8 * 8, "scale": head ** -0.5, "mask": {"size": window},
+              "rot": {"base": 10000.0, "dims": rot_dim,
+                      "scaling": {"factor": 4.0, "original": 4096, "fast": 32.0, "slow": 1.0}}}
+    left = {"heads": heads, "kv_heads": kv_heads, "dim": head, "vdim": head, "scale": head ** -0.5,
+            "mask": {"size": window}, "rot": {"base": base["rope_theta"], "dims": head // 2}}
+    both = {"left": left, "right": {"heads": max(1, kv_heads * head // 64), "dim": 64}, "left_scale": 1.0,
+            "right_scale": 1.0}
+    pattern = [{"type": "latent_attention", "mixer": latent, "mlp": mlp}, {"type": "parallel", "mixer": both, "mlp": mlp}]
+    entries = [copy.deepcopy(pattern[index % len(pattern)]) for index in range(base["num_hidden_layers"])]
+    return {"architecture": "Mamivik", "vocab": base["vocab_size"], "width": width, "norm": {"eps": 1e-6},
+            "canon": {"taps": 4}, "layers": entries, "max_position_embeddings": base["max_position_embeddings"]}
+
+
+def _mamivik_tiny() -> Dict[str, Any]:
+    """A tiny Mamivik configuration for smoke runs of the command lines: both kinds of layer, a
+    layer without feed-forward."""
+    layers = [
+        {"type": "parallel", "mixer": {
+            "left": {"heads": 4, "kv_heads": 2, "dim": 16, "vdim": 16, "scale": 0.25, "mask": {"size": 24},
+                     "rot": {"base": 10000.0, "dims": 8}},
+            "right": {"heads": 2, "dim": 16}, "left_scale": 1.1, "right_scale": 0.8},
+         "mlp": {"kind": "dense", "ff": 160}},
+        {"type": "latent_attention", "mixer": {
+            "heads": 4, "dim": 16, "rot_dim": 8, "vdim": 24, "kv_rank": 40, "q_rank": 32, "scale": 0.2,
+            "mask": {"size": 40}, "rot": {"base": 1000.0, "dims": 8,
+                                           "scaling": {"factor": 2.0, "original": 64, "fast": 8.0, "slow": 1.0}}},
+         "mlp": None},
+        {"type": "parallel", "mixer": {
+            "left": {"heads": 2, "kv_heads": 2, "dim": 32, "vdim": 32, "scale": 0.18, "mask": {"size": 100},
+                     "rot": {"base": 500.0, "dims": 32}},
+            "right": {"heads": 1, "dim": 32}, "left_scale": 0.9, "right_scale": 1.2},
+         "mlp": {"kind": "dense", "ff": 96}},
+    ]
+    return {"architecture": "Mamivik", "vocab": 384, "width": 128, "norm": {"eps": 1e-5}, "canon": {"taps": 3},
+            "layers": layers, "max_position_embeddings": 512}
+
+
 MODEL_SIZES.update({
+    "tiny-m": _mamivik_tiny(),
+    "mamivik-0.5b": _mamivik("0.5b"),
+    "mamivik-1.5b": _mamivik("1.5b"),
+    "mamivik-3b": _mamivik("3b"),
     "tiny-r": _redalix_tiny(),
     "redalix-0.5b": _redalix("0.5b"),
     "redalix-1.5b": _redalix("1.5b"),
