@@ -142,9 +142,12 @@ def test_delta_rule_scan_in_portions(dtype, heads, dim):
         lg = torch.cat([logit[s][done[s] : done[s] + n] for s, n in zip(live, sizes)]).cuda()
         out = torch.zeros(rows.shape[0], inner).cuda()
         q_start, q_len, seq_slots = step_arrays(sizes, [slots[s] for s in live])
+        packed = torch.zeros(rows.shape[0], kernels.delta_rule_packed_width(heads, dim, dim)).cuda()
+        status = torch.zeros(4, dtype=torch.int32).cuda()
         kernels.delta_rule_scan(rows[:, :inner], rows[:, inner : 2 * inner], rows[:, 2 * inner : 3 * inner],
                                 rows[:, 3 * inner : 4 * inner], lg, w0.cuda(), ab.cuda(), decay, key_eps, state, out,
-                                heads, dim, dim, q_start, q_len, seq_slots, len(live))
+                                heads, dim, dim, q_start, q_len, seq_slots, len(live), rows.shape[0], packed, status)
+        assert int(status[0]) == 0
         at = 0
         for s, n in zip(live, sizes):
             got[s][done[s] : done[s] + n] = out[at : at + n].double().cpu().numpy()

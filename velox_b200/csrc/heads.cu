@@ -141,44 +141,98 @@ __global__ void norm_shift_kernel(const float* __restrict__ resid, long long res
 // over the request's own tokens, zeros before its first token.  h of a token of this step is
 // recomputed from its row of the stream; h of the taps - 1 tokens before the portion comes from the
 // request's state row [(taps - 1) x width] (oldest first; zero when a slot is taken).  A value of h
-// is the same float whether it was recomputed or stored: one order of the row's sum, and the
-// products x * r * w made one by one.
-// One block per row, except the first taps - 1 rows of a portion: the block of the portion's first
-// row makes them all, and then writes the portion's last taps - 1 values of h into the state row
-// (entries of a portion shorter than that move up), so nobody else reads or writes the row.
+// is the same float whether it was recomputed or stored: a row's sum of squares is made by one
+// warp in one order, and the products x * r * w one by one.
+// A block takes a tile of NC_ROWS rows of one portion: its warps make the inverse root mean square
+// of the tile's rows and of the taps - 1 rows before them, then all threads write the tile's
+// outputs.  The block of a portion's first tile is the only one that reads the state row, and it
+// writes the portion's last taps - 1 values of h there when its outputs are done (entries of a
+// portion shorter than that move up).  Rows of no request (padding of a rounded step) are tiles of
+// one row without history.
 constexpr int NC_MAX_TAPS = 8;
+constexpr int NC_ROWS = 8;
 
 __device__ __forceinline__ float nc_value(float x, float r, float w) { return __fmul_rn(__fmul_rn(x, r), w); }
 
-__device__ __forceinline__ float nc_inverse_rms(const float* __restrict__ x, int width, float eps, float* scratch) {
+// By one warp: lanes take every 32nd element (or every 32nd pack of four), then the shuffle tree.
+__device__ __forceinline__ float nc_inverse_rms(const float* __restrict__ x, int width, float eps, bool vec) {
+  const int lane = threadIdx.x & 31;
   float ss = 0.f;
-  for (int i = threadIdx.x; i < width; i += blockDim.x) ss = fmaf(x[i], x[i], ss);
-  return rsqrtf(block_sum(ss, scratch) / (float)width + eps);
+  if (vec) {
+    for (int i = lane * 4; i < width; i += 128) {
+      const float4 v = *reinterpret_cast<const float4*>(x + i);
+      ss = fmaf(v.x, v.x, ss);
+      ss = fmaf(v.y, v.y, ss);
+      ss = fmaf(v.z, v.z, ss);
+      ss = fmaf(v.w, v.w, ss);
+    }
+  } else {
+    // The same elements per lane and the same order as the vector form.
+    for (int i = lane * 4; i < width; i += 128)
+      for (int e = 0; e < 4 && i + e < width; ++e) ss = fmaf(x[i + e], x[i + e], ss);
+  }
+  return rsqrtf(warp_sum(ss) / (float)width + eps);
 }
 
-// Row `row` of a portion that starts at stream row `first`: its taps inputs come from the stream
-// (portion index >= 0) or from the old state.
 template <typename T>
-__device__ __forceinline__ void nc_row(const float* __restrict__ resid, long long resid_stride, int width, float eps,
-                                       const float* __restrict__ w, const float* __restrict__ cw, int taps,
-                                       const float* old_state, int first, int row,
-                                       T* __restrict__ out, float* scratch) {
-  float r[NC_MAX_TAPS];
-#pragma unroll
-  for (int j = 0; j < NC_MAX_TAPS; ++j) {
-    r[j] = 0.f;
-    if (j < taps) {
-      const int src = row - (taps - 1) + j;
-      if (src >= 0) r[j] = nc_inverse_rms(resid + (size_t)(first + src) * resid_stride, width, eps, scratch);
+__global__ void __launch_bounds__(256)
+norm_conv_kernel(const float* __restrict__ resid, long long resid_stride, int width, float eps,
+                 const float* __restrict__ w, const float* __restrict__ cw, int taps, float* state,
+                 long long state_stride, T* __restrict__ out, const int* __restrict__ q_start,
+                 const int* __restrict__ q_len, const int* __restrict__ seq_slots, int num_seqs, int num_tokens,
+                 int vec) {
+  __shared__ float inv[NC_ROWS + 2 * NC_MAX_TAPS];
+  allow_dependents();
+  // Which tile this block has: the portions' tiles in the order of the sequences, then one tile
+  // per row that belongs to no sequence.
+  int seq = -1, first = 0, count = 0, tile = 0, covered = 0;
+  {
+    int left = blockIdx.x;
+    for (int s = 0; s < num_seqs && seq < 0; ++s) {
+      const int n = q_len[s];
+      if (n <= 0) continue;
+      const int tiles = (n + NC_ROWS - 1) / NC_ROWS;
+      if (left < tiles) {
+        seq = s;
+        first = q_start[s];
+        count = n;
+        tile = left;
+      } else {
+        left -= tiles;
+      }
+      covered = max(covered, q_start[s] + n);
+    }
+    if (seq < 0) {
+      // Rows behind the last sequence's rows: padding.
+      for (int s = 0; s < num_seqs; ++s) covered = max(covered, q_len[s] > 0 ? q_start[s] + q_len[s] : 0);
+      first = covered + left;
+      if (first >= num_tokens) return;
+      count = 1;
+      tile = 0;
     }
   }
-  for (int i = threadIdx.x; i < width; i += blockDim.x) {
+  grid_dependency_wait();
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, num_warps = blockDim.x >> 5;
+  const int row0 = tile * NC_ROWS;                      // first row of the tile within the portion
+  const int rows = min(NC_ROWS, count - row0);
+  const int halo = min(taps - 1, row0);                 // rows before the tile that are in this step
+  // inv[i]: row (row0 - halo + i) of the portion.
+  for (int i = warp; i < halo + rows; i += num_warps) {
+    const float r = nc_inverse_rms(resid + (size_t)(first + row0 - halo + i) * resid_stride, width, eps, vec != 0);
+    if (lane == 0) inv[i] = r;
+  }
+  __syncthreads();
+  const float* old_state = (seq >= 0 && taps > 1) ? state + (size_t)seq_slots[seq] * state_stride : nullptr;
+  for (int idx = threadIdx.x; idx < rows * width; idx += blockDim.x) {
+    const int lr = idx / width, i = idx - lr * width;
+    const int row = row0 + lr;
+    const float wi = w[i];
     float h = 0.f, acc = 0.f;
 #pragma unroll
     for (int j = 0; j < NC_MAX_TAPS; ++j) {
       if (j < taps) {
         const int src = row - (taps - 1) + j;
-        if (src >= 0) h = nc_value(resid[(size_t)(first + src) * resid_stride + i], r[j], w[i]);
+        if (src >= 0) h = nc_value(resid[(size_t)(first + src) * resid_stride + i], inv[src - (row0 - halo)], wi);
         else h = old_state != nullptr ? old_state[(size_t)(row + j) * width + i] : 0.f;
         acc = fmaf(cw[(size_t)i * taps + j], h, acc);
       }
@@ -186,52 +240,26 @@ __device__ __forceinline__ void nc_row(const float* __restrict__ resid, long lon
     // h is now the row's own value (j = taps - 1).
     out[(size_t)(first + row) * width + i] = from_float<T>(h + acc);
   }
-}
-
-template <typename T>
-__global__ void norm_conv_kernel(const float* __restrict__ resid, long long resid_stride, int width, float eps,
-                                 const float* __restrict__ w, const float* __restrict__ cw, int taps,
-                                 float* state, long long state_stride, T* __restrict__ out,
-                                 const int* __restrict__ q_start, const int* __restrict__ q_len,
-                                 const int* __restrict__ seq_slots, int num_seqs) {
-  __shared__ float scratch[32];
-  allow_dependents();
-  const int t = blockIdx.x;
-  int seq = -1, first = t, count = 1;
-  for (int s = 0; s < num_seqs; ++s) {
-    const int b = q_start[s], n = q_len[s];
-    if (n > 0 && t >= b && t < b + n) {
-      seq = s;
-      first = b;
-      count = n;
-    }
-  }
-  grid_dependency_wait();
-  const int row = t - first;
-  if (seq < 0) {
-    // A row of no request (padding of a rounded step): no history; nobody looks at it.
-    nc_row<T>(resid, resid_stride, width, eps, w, cw, taps, nullptr, t, 0, out, scratch);
-    return;
-  }
-  if (row >= taps - 1) {
-    nc_row<T>(resid, resid_stride, width, eps, w, cw, taps, nullptr, first, row, out, scratch);
-    return;
-  }
-  if (row != 0) return;  // made by the block of the portion's first row
-  float* mine = state + (size_t)seq_slots[seq] * state_stride;
-  const int head_rows = min(taps - 1, count);
-  for (int i = 0; i < head_rows; ++i)
-    nc_row<T>(resid, resid_stride, width, eps, w, cw, taps, mine, first, i, out, scratch);
+  if (seq < 0 || tile != 0 || taps < 2) return;
   // New state: entry e is h of portion index count - (taps - 1) + e; a negative index is the old
   // entry count + e, which lies above e, and a thread moves its own channels in rising e.
-  for (int e = 0; e < taps - 1; ++e) {
-    const int src = count - (taps - 1) + e;
+  __syncthreads();
+  float* mine = state + (size_t)seq_slots[seq] * state_stride;
+  const int tail0 = count - (taps - 1);                 // portion index of entry 0
+  for (int e = warp; e < taps - 1; e += num_warps) {
+    const int src = tail0 + e;
     if (src >= 0) {
-      const float* x = resid + (size_t)(first + src) * resid_stride;
-      const float r = nc_inverse_rms(x, width, eps, scratch);
-      for (int i = threadIdx.x; i < width; i += blockDim.x) mine[(size_t)e * width + i] = nc_value(x[i], r, w[i]);
-    } else {
-      for (int i = threadIdx.x; i < width; i += blockDim.x) mine[(size_t)e * width + i] = mine[(size_t)(count + e) * width + i];
+      const float r = nc_inverse_rms(resid + (size_t)(first + src) * resid_stride, width, eps, vec != 0);
+      if (lane == 0) inv[NC_ROWS + NC_MAX_TAPS + e] = r;
+    }
+  }
+  __syncthreads();
+  for (int i = threadIdx.x; i < width; i += blockDim.x) {
+    for (int e = 0; e < taps - 1; ++e) {
+      const int src = tail0 + e;
+      mine[(size_t)e * width + i] = src >= 0
+          ? nc_value(resid[(size_t)(first + src) * resid_stride + i], inv[NC_ROWS + NC_MAX_TAPS + e], w[i])
+          : mine[(size_t)(count + e) * width + i];
     }
   }
 }
@@ -794,9 +822,12 @@ VX_API int vx_norm_conv(const float* resid, long long resid_stride, int width, f
   if (num_tokens <= 0) return 0;
   if (taps < 1 || taps > NC_MAX_TAPS) return -1;
   if (taps > 1 && (state == nullptr || state_stride < (long long)(taps - 1) * width)) return (int)cudaErrorInvalidValue;
-  VX_BY_DTYPE(dtype, launch_pdl(norm_conv_kernel<T>, dim3(num_tokens), dim3(row_threads(width)), 0, stream, resid,
-                                resid_stride, width, eps, w, conv_w, taps, state, state_stride, (T*)out, q_start,
-                                q_len, seq_slots, num_seqs));
+  // Tiles: at most one per NC_ROWS rows and one more per sequence, or one per row of padding.
+  const int blocks = num_tokens;
+  const int vec = width % 4 == 0 && resid_stride % 4 == 0 && aligned16(resid);
+  VX_BY_DTYPE(dtype, launch_pdl(norm_conv_kernel<T>, dim3(blocks), dim3(256), 0, stream, resid, resid_stride, width,
+                                eps, w, conv_w, taps, state, state_stride, (T*)out, q_start, q_len, seq_slots,
+                                num_seqs, num_tokens, vec));
   return (int)cudaGetLastError();
 }
 

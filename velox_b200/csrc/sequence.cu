@@ -547,104 +547,171 @@ __global__ void ssd_combine_kernel(float* __restrict__ state, long long state_st
 //     w_t = exp(-decay * sigmoid(wl_t + w0)),   a_t = sigmoid(al_t + a_bias),
 //     u_t = k_t / sqrt(sum(k_t^2) + key_eps)
 //     S_t = diag(w_t) S_(t-1) - (a_t * u_t) (u_t^T S_(t-1)) + k_t v_t^T,     o_t = S_t^T r_t
-// Both middle terms read the old state.  A column of S (one value channel) never meets another
-// column, so a block takes CB columns of one head of one sequence; RL lanes share a column, each
-// with DR_KP rows of it in registers, and the two sums over the rows (u^T S and S^T r) meet by
-// shuffles.  The token's vectors over the key channels are made once per block for a tile of
-// tokens (decay, removal rate and unit key in float32) and read from shared memory by every
-// column.  The state is stored [head][column][row], so a thread's rows are contiguous.
-constexpr int DR_KP = 16;
+// Both middle terms read the old state.  Two kernels.
+//
+// delta_rule_prepare_kernel: a warp per (token, head) makes the token's vectors over the key
+// channels in float32 (decay, removal rate times unit key, unit key, key, receptance) and copies
+// the values, into packed rows [head][token]: [w | a u | u | k | r] of KD floats each (Dk padded
+// with zeros to the lanes' rows) and then v (Dv padded to a multiple of four).  A head's rows of
+// consecutive tokens are contiguous, so a tile of tokens is one bulk copy.
+//
+// delta_rule_scan_kernel: a column of S (one value channel) never meets another column, so a
+// block takes CB columns of one head of one sequence; RL lanes share a column, each with KP rows
+// of it in registers, and the two sums over the rows (u^T S and S^T r) meet by shuffles.  Every
+// token waits for the token before it, and a warp alone on its scheduler issues an instruction
+// every five to six cycles, so what counts is how few instructions a thread has per token: four
+// rows a thread (sixteen lanes a column) for key sizes up to 128, sixteen rows beyond.  A block
+// asks for more than half of an SM's shared memory, so that no two of the few blocks share an SM.  The
+// tokens' packed rows come in tiles of TT tokens, one bulk copy a tile, into a ring of two stages,
+// each with its mbarrier, so the next tile arrives while this one is worked through.  The state is
+// stored [head][column][row]: a thread's rows are contiguous.  Every sum has a fixed order, so a
+// token's result does not depend on how the sequence was cut into steps.
+constexpr int DR_KP_SMALL = 4, DR_KP_LARGE = 16, DR_SMALL_MAX_DK = 128;
+constexpr size_t DR_MIN_SMEM = 116 * 1024;
 
 template <typename T>
-__global__ void delta_rule_scan_kernel(const T* __restrict__ r_in, const T* __restrict__ k_in, const T* __restrict__ v_in,
-                                       const T* __restrict__ a_in, long long in_stride, const T* __restrict__ w_in,
-                                       long long w_stride, const float* __restrict__ w0,
-                                       const float* __restrict__ a_bias, float decay, float key_eps,
-                                       float* __restrict__ state, long long state_stride, float* __restrict__ out,
-                                       long long out_stride, int Dk, int Dv, int RL, int CB, int TT,
-                                       const int* __restrict__ q_start, const int* __restrict__ q_len,
-                                       const int* __restrict__ seq_slots) {
-  extern __shared__ __align__(16) float dr_smem[];
+__global__ void __launch_bounds__(256)
+delta_rule_prepare_kernel(const T* __restrict__ r_in, const T* __restrict__ k_in, const T* __restrict__ v_in,
+                          const T* __restrict__ a_in, long long in_stride, const T* __restrict__ w_in,
+                          long long w_stride, const float* __restrict__ w0, const float* __restrict__ a_bias,
+                          float decay, float key_eps, float* __restrict__ packed, long long head_stride,
+                          int heads, int Dk, int Dv, int KD, int Dvp, int num_tokens) {
   allow_dependents();
+  grid_dependency_wait();
+  const int lane = threadIdx.x & 31;
+  const long long unit = (long long)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+  if (unit >= (long long)num_tokens * heads) return;
+  const int t = (int)(unit / heads), h = (int)(unit - (long long)t * heads);
+  const size_t hk = (size_t)h * Dk;
+  const T* k_row = k_in + (size_t)t * in_stride + hk;
+  float ss = 0.f;
+  for (int ch = lane; ch < Dk; ch += 32) {
+    const float kv = to_float(k_row[ch]);
+    ss = fmaf(kv, kv, ss);
+  }
+  const float inv = 1.0f / sqrtf(warp_sum(ss) + key_eps);
+  float* dst = packed + (size_t)h * head_stride + (size_t)t * (5 * KD + Dvp);
+  for (int ch = lane; ch < KD; ch += 32) {
+    float wv = 0.f, au = 0.f, u = 0.f, kv = 0.f, rv = 0.f;
+    if (ch < Dk) {
+      const size_t at = (size_t)t * in_stride + hk + ch;
+      kv = to_float(k_row[ch]);
+      rv = to_float(r_in[at]);
+      u = kv * inv;
+      au = sq_sigmoid(to_float(a_in[at]) + a_bias[hk + ch]) * u;
+      wv = expf(-decay * sq_sigmoid(to_float(w_in[(size_t)t * w_stride + hk + ch]) + w0[hk + ch]));
+    }
+    dst[ch] = wv;
+    dst[KD + ch] = au;
+    dst[2 * KD + ch] = u;
+    dst[3 * KD + ch] = kv;
+    dst[4 * KD + ch] = rv;
+  }
+  for (int c = lane; c < Dvp; c += 32)
+    dst[5 * KD + c] = c < Dv ? to_float(v_in[(size_t)t * in_stride + (size_t)h * Dv + c]) : 0.f;
+}
+
+template <int DR_KP>
+__global__ void delta_rule_scan_kernel(const float* __restrict__ packed, long long head_stride,
+                                       float* __restrict__ state, long long state_stride, float* __restrict__ out,
+                                       long long out_stride, int Dk, int Dv, int Dvp, int RL, int CB, int TT,
+                                       const int* __restrict__ q_start, const int* __restrict__ q_len,
+                                       const int* __restrict__ seq_slots, int* status) {
+  extern __shared__ __align__(16) float dr_smem[];
+  __shared__ __align__(8) unsigned long long dr_bars[2];
+  // The successor is let in when the scan is over: its blocks would share the few busy SMs'
+  // issue slots with a kernel whose every token waits for the token before it.
   const int seq = blockIdx.x, h = blockIdx.y, tile = blockIdx.z;
   const int n = q_len[seq];
-  if (n <= 0) return;
+  if (n <= 0) {
+    allow_dependents();
+    return;
+  }
   const int t_first = q_start[seq];
-  const int KD = RL * DR_KP;  // key channels padded to the lanes' rows
-  float* s_w = dr_smem;             // [TT][KD] decay
-  float* s_au = s_w + TT * KD;      // [TT][KD] removal rate times unit key
-  float* s_u = s_au + TT * KD;      // [TT][KD] unit key
-  float* s_k = s_u + TT * KD;       // [TT][KD] key
-  float* s_r = s_k + TT * KD;       // [TT][KD] receptance
-  float* s_v = s_r + TT * KD;       // [TT][CB] this block's value channels
+  const int KD = RL * DR_KP;
+  const int vec = 5 * KD;                       // floats of a token's vectors over the key channels
+  const int token_floats = vec + Dvp;
   const int p = threadIdx.x % RL, c = threadIdx.x / RL;
   const int col = tile * CB + c;
   const bool live = col < Dv;
-  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, num_warps = blockDim.x >> 5;
   float* mine = state + (size_t)seq_slots[seq] * state_stride + ((size_t)h * Dv + (live ? col : 0)) * Dk;
-  float S[DR_KP];
+  const uint32_t bar0 = smem_u32(&dr_bars[0]), bar1 = smem_u32(&dr_bars[1]);
+  if (threadIdx.x == 0) {
+    mbar_init(bar0, 1);
+    mbar_init(bar1, 1);
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+  }
+  __syncthreads();
+  const int num_tiles = (n + TT - 1) / TT;
+  const float* src_base = packed + (size_t)h * head_stride + (size_t)t_first * token_floats;
+  auto issue = [&](int index) {
+    const int stage = index & 1;
+    const int tt = min(TT, n - index * TT);
+    const uint32_t bar = stage ? bar1 : bar0;
+    const uint32_t bytes = (uint32_t)tt * (uint32_t)token_floats * 4u;
+    mbar_expect_tx(bar, bytes);
+    bulk_copy_g2s(smem_u32(dr_smem + (size_t)stage * TT * token_floats),
+                  src_base + (size_t)index * TT * token_floats, bytes, bar);
+  };
   grid_dependency_wait();
+  if (threadIdx.x == 0) {
+    issue(0);
+    if (num_tiles > 1) issue(1);
+  }
+  float S[DR_KP];
 #pragma unroll
   for (int q = 0; q < DR_KP; ++q) {
     const int row = p * DR_KP + q;
     S[q] = (live && row < Dk) ? mine[row] : 0.f;
   }
-  const size_t hk = (size_t)h * Dk;
-  for (int t0 = 0; t0 < n; t0 += TT) {
-    const int tt = min(TT, n - t0);
-    __syncthreads();
-    for (int idx = threadIdx.x; idx < tt * KD; idx += blockDim.x) {
-      const int i = idx / KD, ch = idx - i * KD;
-      float wv = 0.f, av = 0.f, kv = 0.f, rv = 0.f;
-      if (ch < Dk) {
-        const size_t at = (size_t)(t_first + t0 + i) * in_stride + hk + ch;
-        kv = to_float(k_in[at]);
-        rv = to_float(r_in[at]);
-        av = sq_sigmoid(to_float(a_in[at]) + a_bias[hk + ch]);
-        wv = expf(-decay * sq_sigmoid(to_float(w_in[(size_t)(t_first + t0 + i) * w_stride + hk + ch]) + w0[hk + ch]));
-      }
-      s_w[idx] = wv;
-      s_au[idx] = av;
-      s_k[idx] = kv;
-      s_r[idx] = rv;
-    }
-    for (int idx = threadIdx.x; idx < tt * CB; idx += blockDim.x) {
-      const int i = idx / CB, cc = idx - i * CB;
-      const int vc = tile * CB + cc;
-      s_v[idx] = vc < Dv ? to_float(v_in[(size_t)(t_first + t0 + i) * in_stride + (size_t)h * Dv + vc]) : 0.f;
-    }
-    __syncthreads();
-    // Unit keys: a warp per token, the sum over the key channels in a fixed order.
-    for (int i = warp; i < tt; i += num_warps) {
-      float ss = 0.f;
-      for (int ch = lane; ch < KD; ch += 32) ss = fmaf(s_k[i * KD + ch], s_k[i * KD + ch], ss);
-      ss = warp_sum(ss);
-      const float inv = 1.0f / sqrtf(ss + key_eps);
-      for (int ch = lane; ch < KD; ch += 32) {
-        const float u = s_k[i * KD + ch] * inv;
-        s_u[i * KD + ch] = u;
-        s_au[i * KD + ch] *= u;
-      }
-    }
-    __syncthreads();
+  // One pass over the rows per token makes both sums that read the state as it is before the
+  // token's update: u_t^T S for this token and S^T r for the token before (whose update is the last
+  // one S has seen).  Their shuffle trees run side by side.  `pending` says that a token's output is
+  // still to be made; r_prev are its receptance values for this thread's rows.
+  float r_prev[DR_KP];
+#pragma unroll
+  for (int q = 0; q < DR_KP; ++q) r_prev[q] = 0.f;
+  bool pending = false;
+  int pending_row = 0;
+  for (int index = 0; index < num_tiles; ++index) {
+    const int stage = index & 1;
+    const int tt = min(TT, n - index * TT);
+    mbar_wait(stage ? bar1 : bar0, (uint32_t)(index >> 1) & 1u, status);
+    const float* buf = dr_smem + (size_t)stage * TT * token_floats;
+#pragma unroll 2
     for (int i = 0; i < tt; ++i) {
-      const float4* u4 = reinterpret_cast<const float4*>(s_u + i * KD + p * DR_KP);
-      const float4* w4 = reinterpret_cast<const float4*>(s_w + i * KD + p * DR_KP);
-      const float4* a4 = reinterpret_cast<const float4*>(s_au + i * KD + p * DR_KP);
-      const float4* k4 = reinterpret_cast<const float4*>(s_k + i * KD + p * DR_KP);
-      const float4* r4 = reinterpret_cast<const float4*>(s_r + i * KD + p * DR_KP);
-      float us = 0.f;
+      const float* tok = buf + i * token_floats + p * DR_KP;
+      const float4* w4 = reinterpret_cast<const float4*>(tok);
+      const float4* a4 = reinterpret_cast<const float4*>(tok + KD);
+      const float4* u4 = reinterpret_cast<const float4*>(tok + 2 * KD);
+      const float4* k4 = reinterpret_cast<const float4*>(tok + 3 * KD);
+      const float4* r4 = reinterpret_cast<const float4*>(tok + 4 * KD);
+      float us0 = 0.f, us1 = 0.f, us2 = 0.f, us3 = 0.f;
+      float o0 = 0.f, o1 = 0.f, o2 = 0.f, o3 = 0.f;
 #pragma unroll
       for (int q = 0; q < DR_KP / 4; ++q) {
         const float4 u = u4[q];
-        us = fmaf(u.x, S[4 * q], us);
-        us = fmaf(u.y, S[4 * q + 1], us);
-        us = fmaf(u.z, S[4 * q + 2], us);
-        us = fmaf(u.w, S[4 * q + 3], us);
+        us0 = fmaf(u.x, S[4 * q], us0);
+        us1 = fmaf(u.y, S[4 * q + 1], us1);
+        us2 = fmaf(u.z, S[4 * q + 2], us2);
+        us3 = fmaf(u.w, S[4 * q + 3], us3);
+        o0 = fmaf(S[4 * q], r_prev[4 * q], o0);
+        o1 = fmaf(S[4 * q + 1], r_prev[4 * q + 1], o1);
+        o2 = fmaf(S[4 * q + 2], r_prev[4 * q + 2], o2);
+        o3 = fmaf(S[4 * q + 3], r_prev[4 * q + 3], o3);
       }
-      for (int off = RL >> 1; off > 0; off >>= 1) us += __shfl_xor_sync(0xffffffffu, us, off);
-      const float vj = s_v[i * CB + c];
-      float o = 0.f;
+      float us = (us0 + us1) + (us2 + us3);
+      float o = (o0 + o1) + (o2 + o3);
+#pragma unroll
+      for (int off = 16; off > 0; off >>= 1) {
+        if (off < RL) {
+          us += __shfl_xor_sync(0xffffffffu, us, off);
+          o += __shfl_xor_sync(0xffffffffu, o, off);
+        }
+      }
+      if (pending && live && p == 0) out[(size_t)pending_row * out_stride + (size_t)h * Dv + col] = o;
+      const float vj = buf[i * token_floats + vec + (live ? col : 0)];
 #pragma unroll
       for (int q = 0; q < DR_KP / 4; ++q) {
         const float4 w = w4[q], a = a4[q], k = k4[q], r = r4[q];
@@ -652,15 +719,34 @@ __global__ void delta_rule_scan_kernel(const T* __restrict__ r_in, const T* __re
         S[4 * q + 1] = fmaf(w.y, S[4 * q + 1], fmaf(-a.y, us, k.y * vj));
         S[4 * q + 2] = fmaf(w.z, S[4 * q + 2], fmaf(-a.z, us, k.z * vj));
         S[4 * q + 3] = fmaf(w.w, S[4 * q + 3], fmaf(-a.w, us, k.w * vj));
-        o = fmaf(S[4 * q], r.x, o);
-        o = fmaf(S[4 * q + 1], r.y, o);
-        o = fmaf(S[4 * q + 2], r.z, o);
-        o = fmaf(S[4 * q + 3], r.w, o);
+        r_prev[4 * q] = r.x;
+        r_prev[4 * q + 1] = r.y;
+        r_prev[4 * q + 2] = r.z;
+        r_prev[4 * q + 3] = r.w;
       }
-      for (int off = RL >> 1; off > 0; off >>= 1) o += __shfl_xor_sync(0xffffffffu, o, off);
-      if (live && p == 0) out[(size_t)(t_first + t0 + i) * out_stride + (size_t)h * Dv + col] = o;
+      pending = true;
+      pending_row = t_first + index * TT + i;
     }
+    __syncthreads();  // every thread is done with this stage before it is filled again
+    if (threadIdx.x == 0 && index + 2 < num_tiles) issue(index + 2);
   }
+  {
+    // The last token's output, from the state as it is now.
+    float o0 = 0.f, o1 = 0.f, o2 = 0.f, o3 = 0.f;
+#pragma unroll
+    for (int q = 0; q < DR_KP / 4; ++q) {
+      o0 = fmaf(S[4 * q], r_prev[4 * q], o0);
+      o1 = fmaf(S[4 * q + 1], r_prev[4 * q + 1], o1);
+      o2 = fmaf(S[4 * q + 2], r_prev[4 * q + 2], o2);
+      o3 = fmaf(S[4 * q + 3], r_prev[4 * q + 3], o3);
+    }
+    float o = (o0 + o1) + (o2 + o3);
+#pragma unroll
+    for (int off = 16; off > 0; off >>= 1)
+      if (off < RL) o += __shfl_xor_sync(0xffffffffu, o, off);
+    if (pending && live && p == 0) out[(size_t)pending_row * out_stride + (size_t)h * Dv + col] = o;
+  }
+  allow_dependents();
   if (live) {
 #pragma unroll
     for (int q = 0; q < DR_KP; ++q) {
@@ -997,30 +1083,74 @@ static int dr_pow2_at_least(int v) {
   return p;
 }
 
+// Floats of one token's packed row (all heads), or -1 for a key size beyond the lanes of a warp.
+static int dr_rows_per_lane(int Dk) { return Dk <= DR_SMALL_MAX_DK ? DR_KP_SMALL : DR_KP_LARGE; }
+
+VX_API int vx_delta_rule_packed_width(int heads, int Dk, int Dv) {
+  const int KP = dr_rows_per_lane(Dk);
+  const int RL = dr_pow2_at_least((Dk + KP - 1) / KP);
+  if (RL > 32) return -1;
+  return heads * (5 * RL * KP + (Dv + 3) / 4 * 4);
+}
+
+template <int KP>
+static int dr_launch_scan(const float* packed, long long head_stride, float* state, long long state_stride,
+                          float* out, long long out_stride, int heads, int Dk, int Dv, int Dvp, int RL,
+                          const int* q_start, const int* q_len, const int* seq_slots, int num_seqs, int* status,
+                          cudaStream_t stream) {
+  const int KD = RL * KP;
+  // Columns a block: four warps' worth where the lanes allow, a whole number of warps at least.
+  int CB = 128 / RL;
+  if (CB > 32) CB = 32;
+  if (CB < 1) CB = 1;
+  const int TT = KD <= 64 ? 16 : (KD <= 128 ? 8 : 4);
+  size_t smem = sizeof(float) * 2 * (size_t)TT * (5 * KD + Dvp);
+  const dim3 grid(num_seqs, heads, (Dv + CB - 1) / CB);
+  // Few blocks (a prompt's portion): each gets an SM of its own.  Many blocks (single tokens of
+  // many sequences) share the SMs as they fit.
+  static int num_sms = 0;
+  if (num_sms == 0) {
+    int device = 0;
+    cudaGetDevice(&device);
+    cudaDeviceGetAttribute(&num_sms, cudaDevAttrMultiProcessorCount, device);
+  }
+  if ((long long)grid.x * grid.y * grid.z <= num_sms && smem < DR_MIN_SMEM) smem = DR_MIN_SMEM;
+  static size_t allowed[2] = {0, 0};
+  size_t& limit = allowed[KP == DR_KP_SMALL ? 0 : 1];
+  if (smem > 48 * 1024 && smem > limit) {
+    cudaFuncSetAttribute(delta_rule_scan_kernel<KP>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    limit = smem;
+  }
+  launch_pdl(delta_rule_scan_kernel<KP>, grid, dim3(CB * RL), smem, stream, packed, head_stride, state, state_stride,
+             out, out_stride, Dk, Dv, Dvp, RL, CB, TT, q_start, q_len, seq_slots, status);
+  return (int)cudaGetLastError();
+}
+
 VX_API int vx_delta_rule_scan(const void* r, const void* k, const void* v, const void* a, int dtype, long long in_stride,
                               const void* w, long long w_stride, const float* w0, const float* a_bias, float decay,
-                              float key_eps, float* state, long long state_stride, float* out, long long out_stride,
-                              int heads, int Dk, int Dv, const int* q_start, const int* q_len, const int* seq_slots,
-                              int num_seqs, cudaStream_t stream) {
-  if (num_seqs <= 0) return 0;
+                              float key_eps, float* packed, long long packed_rows, float* state, long long state_stride,
+                              float* out,
+                              long long out_stride, int heads, int Dk, int Dv, const int* q_start, const int* q_len,
+                              const int* seq_slots, int num_seqs, int num_tokens, int* status, cudaStream_t stream) {
+  if (num_seqs <= 0 || num_tokens <= 0) return 0;
   if (heads <= 0 || Dk <= 0 || Dv <= 0) return (int)cudaErrorInvalidValue;
-  const int RL = dr_pow2_at_least((Dk + DR_KP - 1) / DR_KP);
+  const int KP = dr_rows_per_lane(Dk);
+  const int RL = dr_pow2_at_least((Dk + KP - 1) / KP);
   if (RL > 32) return -1;
-  // Columns a block: 32 where the lanes allow, a whole number of warps at least.
-  int CB = 256 / RL;
-  if (CB > 32) CB = 32;
-  const int KD = RL * DR_KP;
-  const int TT = KD <= 64 ? 16 : (KD <= 128 ? 8 : 4);
-  const size_t smem = sizeof(float) * ((size_t)5 * TT * KD + (size_t)TT * CB);
-  const dim3 grid(num_seqs, heads, (Dv + CB - 1) / CB);
-  VX_BY_DTYPE(dtype, {
-    if (smem > 48 * 1024)
-      cudaFuncSetAttribute(delta_rule_scan_kernel<T>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-    launch_pdl(delta_rule_scan_kernel<T>, grid, dim3(CB * RL), smem, stream, (const T*)r, (const T*)k, (const T*)v,
-               (const T*)a, in_stride, (const T*)w, w_stride, w0, a_bias, decay, key_eps, state, state_stride, out,
-               out_stride, Dk, Dv, RL, CB, TT, q_start, q_len, seq_slots);
-  });
-  return (int)cudaGetLastError();
+  const int KD = RL * KP, Dvp = (Dv + 3) / 4 * 4;
+  if (packed_rows < num_tokens) return (int)cudaErrorInvalidValue;
+  const long long packed_stride = packed_rows * (5 * KD + Dvp);  // from one head's rows to the next head's
+  const long long units = (long long)num_tokens * heads;
+  VX_BY_DTYPE(dtype, launch_pdl(delta_rule_prepare_kernel<T>, dim3((unsigned)((units + 7) / 8)), dim3(256), 0, stream,
+                                (const T*)r, (const T*)k, (const T*)v, (const T*)a, in_stride, (const T*)w, w_stride,
+                                w0, a_bias, decay, key_eps, packed, packed_stride, heads, Dk, Dv, KD, Dvp, num_tokens));
+  int code = (int)cudaGetLastError();
+  if (code != 0) return code;
+  if (KP == DR_KP_SMALL)
+    return dr_launch_scan<DR_KP_SMALL>(packed, packed_stride, state, state_stride, out, out_stride, heads, Dk, Dv, Dvp,
+                                       RL, q_start, q_len, seq_slots, num_seqs, status, stream);
+  return dr_launch_scan<DR_KP_LARGE>(packed, packed_stride, state, state_stride, out, out_stride, heads, Dk, Dv, Dvp, RL,
+                                     q_start, q_len, seq_slots, num_seqs, status, stream);
 }
 
 VX_API int vx_gated_group_norm(const float* y, long long y_stride, const void* z, int dtype, long long z_stride,

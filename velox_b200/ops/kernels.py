@@ -146,9 +146,11 @@ def mixers():
             _ptr, _c_ll, _ptr, _c_int, _c_ll, _ptr, _c_f, _c_int, _c_int, _ptr, _c_ll, _c_int, _c_int, _ptr,
         ]
         lib.vx_delta_rule_scan.argtypes = [
-            _ptr, _ptr, _ptr, _ptr, _c_int, _c_ll, _ptr, _c_ll, _ptr, _ptr, _c_f, _c_f, _ptr, _c_ll, _ptr, _c_ll,
-            _c_int, _c_int, _c_int, _ptr, _ptr, _ptr, _c_int, _ptr,
+            _ptr, _ptr, _ptr, _ptr, _c_int, _c_ll, _ptr, _c_ll, _ptr, _ptr, _c_f, _c_f, _ptr, _c_ll, _ptr, _c_ll, _ptr,
+            _c_ll, _c_int, _c_int, _c_int, _ptr, _ptr, _ptr, _c_int, _c_int, _ptr, _ptr,
         ]
+        lib.vx_delta_rule_packed_width.argtypes = [_c_int, _c_int, _c_int]
+        lib.vx_delta_rule_packed_width.restype = _c_int
         lib.vx_dual_norm_mean.argtypes = [_ptr, _ptr, _c_int, _ptr, _ptr, _c_f, _c_f, _c_int, _ptr, _ptr, _c_int, _ptr]
         lib.vx_act_rows.argtypes = [_ptr, _c_int, _c_ll, _ptr, _c_ll, _c_int, _c_int, _c_int, _ptr]
         lib.vx_residual_add.argtypes = [_ptr, _ptr, _c_int, _c_ll, _ptr]
@@ -1478,13 +1480,23 @@ def gated_group_norm(y, z, weight, eps, parts, out, num_tokens, gate_after=False
     )
 
 
+def delta_rule_packed_width(heads: int, key_dim: int, value_dim: int) -> int:
+    """float32 values per token of the scratch rows ``delta_rule_scan`` wants."""
+    width = mixers().vx_delta_rule_packed_width(heads, key_dim, value_dim)
+    if width < 0:
+        raise KernelError(f"delta_rule_scan refuses a key size of {key_dim} (at most 512)")
+    return width
+
+
 def delta_rule_scan(r, k, v, a, w, w0, a_bias, decay, key_eps, state, out, heads, key_dim, value_dim, q_start, q_len,
-                    seq_slots, num_seqs) -> None:
+                    seq_slots, num_seqs, num_tokens, packed, status) -> None:
     """The generalized delta rule over each sequence's tokens (csrc/sequence.cu).  ``r``, ``k``,
     ``v``, ``a`` are column ranges of one projection buffer [tokens, *] (heads x key_dim, value_dim for
     v), ``w`` the decay's logits [tokens, heads * key_dim]; ``w0``, ``a_bias`` float32 [heads *
     key_dim]; ``state`` float32, a row per state slot holding [heads, value_dim, key_dim]; ``out``
-    float32 [tokens, heads * value_dim]."""
+    float32 [tokens, heads * value_dim]; ``packed`` float32 scratch [at least tokens,
+    delta_rule_packed_width(...)]: the tokens' vectors as the scan reads them (the kernels lay it
+    out head by head)."""
     stride = _pitched(r, "r")
     if _pitched(k, "k") != stride or _pitched(v, "v") != stride or _pitched(a, "a") != stride:
         raise ValueError("delta_rule_scan: r, k, v and a are columns of one buffer")
@@ -1492,12 +1504,17 @@ def delta_rule_scan(r, k, v, a, w, w0, a_bias, decay, key_eps, state, out, heads
         raise TypeError("delta_rule_scan: logits in the compute dtype, state and out float32")
     _need(w0, torch.float32, "w0")
     _need(a_bias, torch.float32, "a_bias")
+    _need(packed, torch.float32, "packed")
+    _need(status, torch.int32, "status")
     if state.shape[1] < heads * key_dim * value_dim or state.stride(1) != 1:
         raise ValueError("delta_rule_scan: the state row is too small")
+    if packed.shape[0] < num_tokens or packed.shape[1] != delta_rule_packed_width(heads, key_dim, value_dim):
+        raise ValueError("delta_rule_scan: the scratch rows do not fit")
     code = mixers().vx_delta_rule_scan(
         _p(r), _p(k), _p(v), _p(a), _code(r.dtype), stride, _p(w), _pitched(w, "w"), _p(w0), _p(a_bias),
-        float(decay), float(key_eps), _p(state), state.stride(0), _p(out), _pitched(out, "out"), heads, key_dim,
-        value_dim, _p(q_start), _p(q_len), _p(seq_slots), num_seqs, _stream())
+        float(decay), float(key_eps), _p(packed), packed.shape[0], _p(state), state.stride(0), _p(out),
+        _pitched(out, "out"), heads,
+        key_dim, value_dim, _p(q_start), _p(q_len), _p(seq_slots), num_seqs, num_tokens, _p(status), _stream())
     if code == -1:
         raise KernelError(f"delta_rule_scan refuses a key size of {key_dim} (at most 512)")
     _check(code, "delta_rule_scan")

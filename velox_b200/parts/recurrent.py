@@ -263,11 +263,13 @@ class DeltaRule(Mixer):
         logits = ws.get(f"delta_rule.decay{inner}", (ws.max_tokens, inner), self.dtype)
         linear(bent, self.w_decay_up, None, logits, T, status=ctx.status)
         y = ws.get(f"delta_rule.y{inner}", (ws.max_tokens, inner), torch.float32)
+        width = kernels.delta_rule_packed_width(self.heads, self.dim, self.dim)
+        packed = ws.get(f"delta_rule.packed{width}", (ws.max_tokens, width), torch.float32)
         kernels.delta_rule_scan(
             proj[:, :inner], proj[:, inner : 2 * inner], proj[:, 2 * inner : 3 * inner],
             proj[:, 4 * inner : 5 * inner], logits, self.decay_bias, self.removal_bias, self.decay_scale,
             self.key_eps, cache.state, y, self.heads, self.dim, self.dim, ctx.q_start, ctx.q_len, ctx.seq_slots,
-            ctx.num_seqs)
+            ctx.num_seqs, T, packed, ctx.status)
         normed = ws.get(f"delta_rule.normed{inner}", (ws.max_tokens, inner), self.dtype)
         kernels.gated_group_norm(y, proj[:, 3 * inner : 4 * inner], self.norm_w, self.eps, self.heads, normed, T,
                                  gate_after=True)
