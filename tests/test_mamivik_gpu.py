@@ -89,7 +89,7 @@ def test_norm_and_input_convolution_in_portions(dtype, width, taps):
         rows = torch.cat([x[s][done[s] : done[s] + n] for s, n in zip(live, sizes)]).cuda()
         out = torch.zeros(rows.shape[0], width, dtype=dt).cuda()
         q_start, q_len, seq_slots = step_arrays(sizes, [slots[s] for s in live])
-        kernels.norm_conv(rows, w.cuda(), eps, cw.cuda(), state if taps > 1 else None, out, rows.shape[0], q_start,
+        kernels.norm_conv(rows, w.cuda(), eps, cw.t().contiguous().cuda(), state if taps > 1 else None, out, rows.shape[0], q_start,
                           q_len, seq_slots, len(live))
         at = 0
         for s, n in zip(live, sizes):

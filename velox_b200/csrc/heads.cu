@@ -147,8 +147,9 @@ __global__ void norm_shift_kernel(const float* __restrict__ resid, long long res
 // of the tile's rows and of the taps - 1 rows before them, then all threads write the tile's
 // outputs.  The block of a portion's first tile is the only one that reads the state row, and it
 // writes the portion's last taps - 1 values of h there when its outputs are done (entries of a
-// portion shorter than that move up).  Rows of no request (padding of a rounded step) are tiles of
-// one row without history.
+// portion shorter than that move up).  Rows of no request (padding of a rounded step, behind the
+// sequences' rows) come in tiles of rows without history.  The taps are given transposed, [taps x
+// width], so that a tap of neighbouring channels is one load.
 constexpr int NC_MAX_TAPS = 8;
 constexpr int NC_ROWS = 8;
 
@@ -177,45 +178,56 @@ __device__ __forceinline__ float nc_inverse_rms(const float* __restrict__ x, int
 template <typename T>
 __global__ void __launch_bounds__(256)
 norm_conv_kernel(const float* __restrict__ resid, long long resid_stride, int width, float eps,
-                 const float* __restrict__ w, const float* __restrict__ cw, int taps, float* state,
+                 const float* __restrict__ w, const float* __restrict__ cw_t, int taps, float* state,
                  long long state_stride, T* __restrict__ out, const int* __restrict__ q_start,
                  const int* __restrict__ q_len, const int* __restrict__ seq_slots, int num_seqs, int num_tokens,
                  int vec) {
   __shared__ float inv[NC_ROWS + 2 * NC_MAX_TAPS];
+  __shared__ int seq_first[256], seq_count[256];
   allow_dependents();
   // Which tile this block has: the portions' tiles in the order of the sequences, then one tile
-  // per row that belongs to no sequence.
+  // per row behind the last sequence's rows (padding).  The sequences' extents are fetched 256 at
+  // a time, all at once, and then walked in shared memory.
   int seq = -1, first = 0, count = 0, tile = 0, covered = 0;
   {
     int left = blockIdx.x;
-    for (int s = 0; s < num_seqs && seq < 0; ++s) {
-      const int n = q_len[s];
-      if (n <= 0) continue;
-      const int tiles = (n + NC_ROWS - 1) / NC_ROWS;
-      if (left < tiles) {
-        seq = s;
-        first = q_start[s];
-        count = n;
-        tile = left;
-      } else {
-        left -= tiles;
+    for (int base = 0; base < num_seqs && seq < 0; base += 256) {
+      const int here = min(256, num_seqs - base);
+      __syncthreads();
+      if ((int)threadIdx.x < here) {
+        seq_first[threadIdx.x] = q_start[base + threadIdx.x];
+        seq_count[threadIdx.x] = q_len[base + threadIdx.x];
       }
-      covered = max(covered, q_start[s] + n);
+      __syncthreads();
+      for (int s = 0; s < here && seq < 0; ++s) {
+        const int n = seq_count[s];
+        if (n <= 0) continue;
+        const int tiles = (n + NC_ROWS - 1) / NC_ROWS;
+        if (left < tiles) {
+          seq = base + s;
+          first = seq_first[s];
+          count = n;
+          tile = left;
+        } else {
+          left -= tiles;
+        }
+        covered = max(covered, seq_first[s] + n);
+      }
     }
     if (seq < 0) {
-      // Rows behind the last sequence's rows: padding.
-      for (int s = 0; s < num_seqs; ++s) covered = max(covered, q_len[s] > 0 ? q_start[s] + q_len[s] : 0);
-      first = covered + left;
-      if (first >= num_tokens) return;
-      count = 1;
-      tile = 0;
+      // A tile of rows without history: as if each were the first token of a portion of its own.
+      first = covered;
+      tile = left;
+      count = num_tokens - covered;
+      if (tile * NC_ROWS >= count) return;
     }
   }
+  const bool lonely = seq < 0;
   grid_dependency_wait();
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, num_warps = blockDim.x >> 5;
   const int row0 = tile * NC_ROWS;                      // first row of the tile within the portion
   const int rows = min(NC_ROWS, count - row0);
-  const int halo = min(taps - 1, row0);                 // rows before the tile that are in this step
+  const int halo = lonely ? 0 : min(taps - 1, row0);    // rows before the tile that are in this step
   // inv[i]: row (row0 - halo + i) of the portion.
   for (int i = warp; i < halo + rows; i += num_warps) {
     const float r = nc_inverse_rms(resid + (size_t)(first + row0 - halo + i) * resid_stride, width, eps, vec != 0);
@@ -223,22 +235,68 @@ norm_conv_kernel(const float* __restrict__ resid, long long resid_stride, int wi
   }
   __syncthreads();
   const float* old_state = (seq >= 0 && taps > 1) ? state + (size_t)seq_slots[seq] * state_stride : nullptr;
-  for (int idx = threadIdx.x; idx < rows * width; idx += blockDim.x) {
-    const int lr = idx / width, i = idx - lr * width;
-    const int row = row0 + lr;
-    const float wi = w[i];
-    float h = 0.f, acc = 0.f;
+  if (vec && (reinterpret_cast<uintptr_t>(old_state) & 15) == 0 && state_stride % 4 == 0 &&
+      (reinterpret_cast<uintptr_t>(cw_t) & 15) == 0 && (reinterpret_cast<uintptr_t>(w) & 15) == 0) {
+    // Four channels a thread: every load of a pack's taps is under way before the first product.
+    const int packs = width >> 2;
+    for (int idx = threadIdx.x; idx < rows * packs; idx += blockDim.x) {
+      const int lr = idx / packs, i = (idx - lr * packs) << 2;
+      const int row = row0 + lr;
+      float4 x[NC_MAX_TAPS];
+      float r[NC_MAX_TAPS];
 #pragma unroll
-    for (int j = 0; j < NC_MAX_TAPS; ++j) {
-      if (j < taps) {
-        const int src = row - (taps - 1) + j;
-        if (src >= 0) h = nc_value(resid[(size_t)(first + src) * resid_stride + i], inv[src - (row0 - halo)], wi);
-        else h = old_state != nullptr ? old_state[(size_t)(row + j) * width + i] : 0.f;
-        acc = fmaf(cw[(size_t)i * taps + j], h, acc);
+      for (int j = 0; j < NC_MAX_TAPS; ++j) {
+        if (j < taps) {
+          const int src = (lonely && j < taps - 1) ? -1 : row - (taps - 1) + j;
+          if (src >= 0) {
+            x[j] = *reinterpret_cast<const float4*>(resid + (size_t)(first + src) * resid_stride + i);
+            r[j] = inv[src - (row0 - halo)];
+          } else {
+            x[j] = old_state != nullptr ? *reinterpret_cast<const float4*>(old_state + (size_t)(row + j) * width + i)
+                                        : make_float4(0.f, 0.f, 0.f, 0.f);
+            r[j] = -1.f;  // a stored value: taken as it is
+          }
+        }
       }
+      const float4 wi = *reinterpret_cast<const float4*>(w + i);
+      float h[4] = {0.f, 0.f, 0.f, 0.f}, acc[4] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+      for (int j = 0; j < NC_MAX_TAPS; ++j) {
+        if (j < taps) {
+          const float4 tap = *reinterpret_cast<const float4*>(cw_t + (size_t)j * width + i);
+          const float xs[4] = {x[j].x, x[j].y, x[j].z, x[j].w};
+          const float ws[4] = {wi.x, wi.y, wi.z, wi.w};
+          const float ts[4] = {tap.x, tap.y, tap.z, tap.w};
+#pragma unroll
+          for (int c = 0; c < 4; ++c) {
+            h[c] = r[j] < 0.f ? xs[c] : nc_value(xs[c], r[j], ws[c]);
+            acc[c] = fmaf(ts[c], h[c], acc[c]);
+          }
+        }
+      }
+      float result[4] = {h[0] + acc[0], h[1] + acc[1], h[2] + acc[2], h[3] + acc[3]};
+      T* dst = out + (size_t)(first + row) * width + i;
+#pragma unroll
+      for (int c = 0; c < 4; ++c) dst[c] = from_float<T>(result[c]);
     }
-    // h is now the row's own value (j = taps - 1).
-    out[(size_t)(first + row) * width + i] = from_float<T>(h + acc);
+  } else {
+    for (int idx = threadIdx.x; idx < rows * width; idx += blockDim.x) {
+      const int lr = idx / width, i = idx - lr * width;
+      const int row = row0 + lr;
+      const float wi = w[i];
+      float h = 0.f, acc = 0.f;
+#pragma unroll
+      for (int j = 0; j < NC_MAX_TAPS; ++j) {
+        if (j < taps) {
+          const int src = (lonely && j < taps - 1) ? -1 : row - (taps - 1) + j;
+          if (src >= 0) h = nc_value(resid[(size_t)(first + src) * resid_stride + i], inv[src - (row0 - halo)], wi);
+          else h = old_state != nullptr ? old_state[(size_t)(row + j) * width + i] : 0.f;
+          acc = fmaf(cw_t[(size_t)j * width + i], h, acc);
+        }
+      }
+      // h is now the row's own value (j = taps - 1).
+      out[(size_t)(first + row) * width + i] = from_float<T>(h + acc);
+    }
   }
   if (seq < 0 || tile != 0 || taps < 2) return;
   // New state: entry e is h of portion index count - (taps - 1) + e; a negative index is the old
@@ -249,18 +307,28 @@ norm_conv_kernel(const float* __restrict__ resid, long long resid_stride, int wi
   for (int e = warp; e < taps - 1; e += num_warps) {
     const int src = tail0 + e;
     if (src >= 0) {
-      const float r = nc_inverse_rms(resid + (size_t)(first + src) * resid_stride, width, eps, vec != 0);
+      // A row of this tile has its statistic already (the same sum, made once).
+      const float r = src < rows ? inv[src]
+                                 : nc_inverse_rms(resid + (size_t)(first + src) * resid_stride, width, eps, vec != 0);
       if (lane == 0) inv[NC_ROWS + NC_MAX_TAPS + e] = r;
     }
   }
   __syncthreads();
   for (int i = threadIdx.x; i < width; i += blockDim.x) {
-    for (int e = 0; e < taps - 1; ++e) {
-      const int src = tail0 + e;
-      mine[(size_t)e * width + i] = src >= 0
-          ? nc_value(resid[(size_t)(first + src) * resid_stride + i], inv[NC_ROWS + NC_MAX_TAPS + e], w[i])
-          : mine[(size_t)(count + e) * width + i];
+    // All of a channel's new entries are read before the first is written.
+    float fresh[NC_MAX_TAPS];
+#pragma unroll
+    for (int e = 0; e < NC_MAX_TAPS - 1; ++e) {
+      if (e < taps - 1) {
+        const int src = tail0 + e;
+        fresh[e] = src >= 0
+            ? nc_value(resid[(size_t)(first + src) * resid_stride + i], inv[NC_ROWS + NC_MAX_TAPS + e], w[i])
+            : mine[(size_t)(count + e) * width + i];
+      }
     }
+#pragma unroll
+    for (int e = 0; e < NC_MAX_TAPS - 1; ++e)
+      if (e < taps - 1) mine[(size_t)e * width + i] = fresh[e];
   }
 }
 
@@ -822,8 +890,8 @@ VX_API int vx_norm_conv(const float* resid, long long resid_stride, int width, f
   if (num_tokens <= 0) return 0;
   if (taps < 1 || taps > NC_MAX_TAPS) return -1;
   if (taps > 1 && (state == nullptr || state_stride < (long long)(taps - 1) * width)) return (int)cudaErrorInvalidValue;
-  // Tiles: at most one per NC_ROWS rows and one more per sequence, or one per row of padding.
-  const int blocks = num_tokens;
+  // Tiles: at most one per NC_ROWS rows, one more per sequence, and one more for the padding.
+  const int blocks = (num_tokens + NC_ROWS - 1) / NC_ROWS + num_seqs + 1;
   const int vec = width % 4 == 0 && resid_stride % 4 == 0 && aligned16(resid);
   VX_BY_DTYPE(dtype, launch_pdl(norm_conv_kernel<T>, dim3(blocks), dim3(256), 0, stream, resid, resid_stride, width,
                                 eps, w, conv_w, taps, state, state_stride, (T*)out, q_start, q_len, seq_slots,

@@ -611,10 +611,10 @@ delta_rule_prepare_kernel(const T* __restrict__ r_in, const T* __restrict__ k_in
     dst[5 * KD + c] = c < Dv ? to_float(v_in[(size_t)t * in_stride + (size_t)h * Dv + c]) : 0.f;
 }
 
-template <int DR_KP>
+template <int DR_KP, int RL>
 __global__ void delta_rule_scan_kernel(const float* __restrict__ packed, long long head_stride,
                                        float* __restrict__ state, long long state_stride, float* __restrict__ out,
-                                       long long out_stride, int Dk, int Dv, int Dvp, int RL, int CB, int TT,
+                                       long long out_stride, int Dk, int Dv, int Dvp, int CB, int TT,
                                        const int* __restrict__ q_start, const int* __restrict__ q_len,
                                        const int* __restrict__ seq_slots, int* status) {
   extern __shared__ __align__(16) float dr_smem[];
@@ -628,8 +628,8 @@ __global__ void delta_rule_scan_kernel(const float* __restrict__ packed, long lo
     return;
   }
   const int t_first = q_start[seq];
-  const int KD = RL * DR_KP;
-  const int vec = 5 * KD;                       // floats of a token's vectors over the key channels
+  constexpr int KD = RL * DR_KP;
+  constexpr int vec = 5 * KD;                   // floats of a token's vectors over the key channels
   const int token_floats = vec + Dvp;
   const int p = threadIdx.x % RL, c = threadIdx.x / RL;
   const int col = tile * CB + c;
@@ -679,9 +679,10 @@ __global__ void delta_rule_scan_kernel(const float* __restrict__ packed, long lo
     const int tt = min(TT, n - index * TT);
     mbar_wait(stage ? bar1 : bar0, (uint32_t)(index >> 1) & 1u, status);
     const float* buf = dr_smem + (size_t)stage * TT * token_floats;
+    const float* tok = buf + p * DR_KP;
+    int row_now = t_first + index * TT;
 #pragma unroll 2
-    for (int i = 0; i < tt; ++i) {
-      const float* tok = buf + i * token_floats + p * DR_KP;
+    for (int i = 0; i < tt; ++i, tok += token_floats, ++row_now) {
       const float4* w4 = reinterpret_cast<const float4*>(tok);
       const float4* a4 = reinterpret_cast<const float4*>(tok + KD);
       const float4* u4 = reinterpret_cast<const float4*>(tok + 2 * KD);
@@ -711,7 +712,7 @@ __global__ void delta_rule_scan_kernel(const float* __restrict__ packed, long lo
         }
       }
       if (pending && live && p == 0) out[(size_t)pending_row * out_stride + (size_t)h * Dv + col] = o;
-      const float vj = buf[i * token_floats + vec + (live ? col : 0)];
+      const float vj = tok[vec - p * DR_KP + (live ? col : 0)];
 #pragma unroll
       for (int q = 0; q < DR_KP / 4; ++q) {
         const float4 w = w4[q], a = a4[q], k = k4[q], r = r4[q];
@@ -725,7 +726,7 @@ __global__ void delta_rule_scan_kernel(const float* __restrict__ packed, long lo
         r_prev[4 * q + 3] = r.w;
       }
       pending = true;
-      pending_row = t_first + index * TT + i;
+      pending_row = row_now;
     }
     __syncthreads();  // every thread is done with this stage before it is filled again
     if (threadIdx.x == 0 && index + 2 < num_tiles) issue(index + 2);
@@ -1093,12 +1094,12 @@ VX_API int vx_delta_rule_packed_width(int heads, int Dk, int Dv) {
   return heads * (5 * RL * KP + (Dv + 3) / 4 * 4);
 }
 
-template <int KP>
+template <int KP, int RL>
 static int dr_launch_scan(const float* packed, long long head_stride, float* state, long long state_stride,
-                          float* out, long long out_stride, int heads, int Dk, int Dv, int Dvp, int RL,
+                          float* out, long long out_stride, int heads, int Dk, int Dv, int Dvp,
                           const int* q_start, const int* q_len, const int* seq_slots, int num_seqs, int* status,
                           cudaStream_t stream) {
-  const int KD = RL * KP;
+  constexpr int KD = RL * KP;
   // Columns a block: four warps' worth where the lanes allow, a whole number of warps at least.
   int CB = 128 / RL;
   if (CB > 32) CB = 32;
@@ -1115,14 +1116,13 @@ static int dr_launch_scan(const float* packed, long long head_stride, float* sta
     cudaDeviceGetAttribute(&num_sms, cudaDevAttrMultiProcessorCount, device);
   }
   if ((long long)grid.x * grid.y * grid.z <= num_sms && smem < DR_MIN_SMEM) smem = DR_MIN_SMEM;
-  static size_t allowed[2] = {0, 0};
-  size_t& limit = allowed[KP == DR_KP_SMALL ? 0 : 1];
+  static size_t limit = 0;  // one per instantiation
   if (smem > 48 * 1024 && smem > limit) {
-    cudaFuncSetAttribute(delta_rule_scan_kernel<KP>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    cudaFuncSetAttribute(delta_rule_scan_kernel<KP, RL>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     limit = smem;
   }
-  launch_pdl(delta_rule_scan_kernel<KP>, grid, dim3(CB * RL), smem, stream, packed, head_stride, state, state_stride,
-             out, out_stride, Dk, Dv, Dvp, RL, CB, TT, q_start, q_len, seq_slots, status);
+  launch_pdl(delta_rule_scan_kernel<KP, RL>, grid, dim3(CB * RL), smem, stream, packed, head_stride, state,
+             state_stride, out, out_stride, Dk, Dv, Dvp, CB, TT, q_start, q_len, seq_slots, status);
   return (int)cudaGetLastError();
 }
 
@@ -1146,11 +1146,20 @@ VX_API int vx_delta_rule_scan(const void* r, const void* k, const void* v, const
                                 w0, a_bias, decay, key_eps, packed, packed_stride, heads, Dk, Dv, KD, Dvp, num_tokens));
   int code = (int)cudaGetLastError();
   if (code != 0) return code;
-  if (KP == DR_KP_SMALL)
-    return dr_launch_scan<DR_KP_SMALL>(packed, packed_stride, state, state_stride, out, out_stride, heads, Dk, Dv, Dvp,
-                                       RL, q_start, q_len, seq_slots, num_seqs, status, stream);
-  return dr_launch_scan<DR_KP_LARGE>(packed, packed_stride, state, state_stride, out, out_stride, heads, Dk, Dv, Dvp, RL,
-                                     q_start, q_len, seq_slots, num_seqs, status, stream);
+#define VX_DR(KPV, RLV)                                                                                          \
+  if (KP == KPV && RL == RLV)                                                                                    \
+    return dr_launch_scan<KPV, RLV>(packed, packed_stride, state, state_stride, out, out_stride, heads, Dk, Dv, Dvp, \
+                                    q_start, q_len, seq_slots, num_seqs, status, stream)
+  VX_DR(DR_KP_SMALL, 1);
+  VX_DR(DR_KP_SMALL, 2);
+  VX_DR(DR_KP_SMALL, 4);
+  VX_DR(DR_KP_SMALL, 8);
+  VX_DR(DR_KP_SMALL, 16);
+  VX_DR(DR_KP_SMALL, 32);
+  VX_DR(DR_KP_LARGE, 16);
+  VX_DR(DR_KP_LARGE, 32);
+#undef VX_DR
+  return -1;
 }
 
 VX_API int vx_gated_group_norm(const float* y, long long y_stride, const void* z, int dtype, long long z_stride,

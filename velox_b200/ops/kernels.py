@@ -1730,22 +1730,23 @@ def add_rows(resid, a, b, num_tokens, scale_a: float = 1.0, scale_b: float = 1.0
            "add_rows")
 
 
-def norm_conv(resid, weight, eps, conv_weight, state, out, num_tokens, q_start, q_len, seq_slots, num_seqs) -> None:
+def norm_conv(resid, weight, eps, conv_weight_t, state, out, num_tokens, q_start, q_len, seq_slots, num_seqs) -> None:
     """``out = h + conv(h)`` with ``h = resid / rms(resid) * weight`` per row and ``conv(h)_t = sum_j
-    conv_weight[:, j] * h_(t - taps + 1 + j)`` over a request's own tokens (zeros before its first).
-    ``state`` float32, a row per state slot: the request's last taps - 1 values of h, oldest first;
-    read for a portion's first rows and then rewritten."""
+    taps[j] * h_(t - taps + 1 + j)`` over a request's own tokens (zeros before its first).
+    ``conv_weight_t`` float32 [taps, width]: the taps, the current token's last.  ``state`` float32,
+    a row per state slot: the request's last taps - 1 values of h, oldest first; read for a
+    portion's first rows and then rewritten."""
     _need(resid, torch.float32, "resid")
     _need(weight, torch.float32, "weight")
-    _need(conv_weight, torch.float32, "conv_weight")
+    _need(conv_weight_t, torch.float32, "conv_weight_t")
     width = resid.shape[1]
-    taps = conv_weight.shape[1]
-    if conv_weight.shape[0] != width or out.shape[1] != width or not out.is_contiguous():
+    taps = conv_weight_t.shape[0]
+    if conv_weight_t.shape[1] != width or out.shape[1] != width or not out.is_contiguous():
         raise ValueError("norm_conv: widths do not agree")
     if taps > 1 and (state is None or state.dtype != torch.float32 or state.stride(-1) != 1
                      or state.shape[1] < (taps - 1) * width):
         raise ValueError("norm_conv needs a float32 state row of (taps - 1) * width values per slot")
-    code = heads().vx_norm_conv(_p(resid), resid.stride(0), width, float(eps), _p(weight), _p(conv_weight), taps,
+    code = heads().vx_norm_conv(_p(resid), resid.stride(0), width, float(eps), _p(weight), _p(conv_weight_t), taps,
                                 _p(state), 0 if state is None else state.stride(0), _p(out), _code(out.dtype),
                                 _p(q_start), _p(q_len), _p(seq_slots), int(num_seqs), int(num_tokens), _stream())
     if code == -1:

@@ -44,6 +44,8 @@ class PreNormBlock:
                                  f"({self.norm_mixer.size}, taps) with 1 to 8 taps")
             if self.norm_mixer.center:
                 raise ValueError("input_conv goes with an RMS norm")
+            # The kernel reads the taps transposed: a tap of neighbouring channels is one load.
+            self.conv_t = self.conv.to(torch.float32).t().contiguous()
             kernels.heads()
 
     def state_needs(self):
@@ -70,7 +72,7 @@ class PreNormBlock:
         if self.conv is not None:
             if hidden.delta is not None:
                 kernels.add_rows(hidden.resid, hidden.delta, None, T)
-            kernels.norm_conv(hidden.resid, self.norm_mixer.weight, self.norm_mixer.eps, self.conv,
+            kernels.norm_conv(hidden.resid, self.norm_mixer.weight, self.norm_mixer.eps, self.conv_t,
                               getattr(cache, "block_state", None), normed, T, ctx.q_start, ctx.q_len, ctx.seq_slots,
                               ctx.num_seqs)
             mixed = self.mixer.forward(normed, ctx, cache)
