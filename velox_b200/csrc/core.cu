@@ -111,6 +111,9 @@ __global__ void add_rmsnorm_kernel(float* __restrict__ resid, const T* __restric
 //   halves (rot = 0: no rotation), cos/sin are float32 tables [max_pos, rot/2].
 //   slots[t] is the flat cache index (page * page_size + offset); a negative slot skips the
 //   write (padding rows).  write_cache = 0 rotates q only (a layer that reads another's cache).
+//   v_from_k: the rows hold [H*D q | G*D k] only and a token's values are its keys as projected,
+//   before the rotation (k is rotated on its way into the cache, not in the row).  row_width is
+//   the pitch of the rows.
 //   One block per (token, head of q|k|v).
 // ---------------------------------------------------------------------------------------------
 template <typename T>
@@ -120,7 +123,7 @@ __global__ void rope_cache_write_kernel(T* __restrict__ qkv, const int* __restri
                                         const int* __restrict__ slots, T* __restrict__ k_cache,
                                         T* __restrict__ v_cache, int H, int G, int D, int rot,
                                         int max_pos, long long num_slots, int write_cache,
-                                        int* status) {
+                                        long long row_width, int v_from_k, int* status) {
   VX_TRACE_SCOPE(3);
   allow_dependents();
   grid_dependency_wait();
@@ -136,8 +139,8 @@ __global__ void rope_cache_write_kernel(T* __restrict__ qkv, const int* __restri
   }
   const float* c = cos_t + (size_t)pos * half;
   const float* s = sin_t + (size_t)pos * half;
-  const size_t width = (size_t)(H + 2 * G) * D;
-  T* row = qkv + (size_t)t * width + (size_t)head * D;
+  const int src_head = (v_from_k && head >= H + G) ? head - G : head;
+  T* row = qkv + (size_t)t * (size_t)row_width + (size_t)src_head * D;
   auto load = [&](int e) { return to_float(row[e]); };
 
   T* dst = row;  // q is rotated in place
@@ -223,7 +226,7 @@ __global__ void rope_cache_write_vec_kernel(T* __restrict__ qkv, const int* __re
                                             const int* __restrict__ slots, T* __restrict__ k_cache,
                                             T* __restrict__ v_cache, int H, int G, int D, int rot,
                                             int max_pos, long long num_slots, int write_cache,
-                                            int* status) {
+                                            long long row_width, int v_from_k, int* status) {
   constexpr int N = Vec16<T>::N;
   VX_TRACE_SCOPE(3);
   allow_dependents();
@@ -239,12 +242,12 @@ __global__ void rope_cache_write_vec_kernel(T* __restrict__ qkv, const int* __re
   const int slot = write_cache ? slots[t] : -1;
   const bool slot_ok = slot >= 0 && (long long)slot < num_slots;
   if (write_cache && slot >= 0 && !slot_ok && threadIdx.x == 0) atomicOr(status, VX_STATUS_BAD_SLOT);
-  T* row = qkv + (size_t)t * (size_t)(H + 2 * G) * D;
+  T* row = qkv + (size_t)t * (size_t)row_width;
   const int total = (H + 2 * G) * chunks;
   for (int idx = threadIdx.x; idx < total; idx += blockDim.x) {
     const int head = idx / chunks, d = (idx - head * chunks) * N;
     const bool is_q = head < H, is_k = !is_q && head < H + G;
-    T* src = row + (size_t)head * D;
+    T* src = row + (size_t)((v_from_k && head >= H + G) ? head - G : head) * D;
     T* dst = src;
     if (!is_q) {
       if (!slot_ok) continue;
@@ -284,7 +287,8 @@ __global__ void rope_cache_write_pair_kernel(T* __restrict__ qkv, const int* __r
                                              const float* __restrict__ cos_t, const float* __restrict__ sin_t,
                                              const int* __restrict__ slots, T* __restrict__ k_cache,
                                              T* __restrict__ v_cache, int H, int G, int D, int max_pos,
-                                             long long num_slots, int write_cache, int num_tokens, int* status) {
+                                             long long num_slots, int write_cache, int num_tokens,
+                                             long long row_width, int v_from_k, int* status) {
   constexpr int N = Vec16<T>::N;
   VX_TRACE_SCOPE(3);
   allow_dependents();
@@ -299,7 +303,7 @@ __global__ void rope_cache_write_pair_kernel(T* __restrict__ qkv, const int* __r
     const int within = (int)(idx - (long long)t * per_token);
     const int head = within / pairs, d = (within - head * pairs) * N;
     const bool is_q = head < H, is_k = !is_q && head < H + G;
-    T* src = qkv + (size_t)t * (size_t)(H + 2 * G) * D + (size_t)head * D;
+    T* src = qkv + (size_t)t * (size_t)row_width + (size_t)((v_from_k && head >= H + G) ? head - G : head) * D;
     T* dst = src;
     if (!is_q) {
       if (!write_cache) continue;
@@ -737,11 +741,12 @@ VX_API int vx_add_rmsnorm(float* resid, const void* delta, const float* weight, 
 VX_API int vx_rope_cache_write(void* qkv, int dtype, const int* positions, const float* cos_t,
                                const float* sin_t, const int* slots, void* k_cache,
                                void* v_cache, int num_tokens, int H, int G, int D, int rot,
-                               int max_pos, long long num_slots, int write_cache, int* status,
-                               cudaStream_t stream) {
+                               int max_pos, long long num_slots, int write_cache, long long row_width,
+                               int v_from_k, int* status, cudaStream_t stream) {
   if (num_tokens <= 0) return 0;
+  if (row_width < (long long)(H + (v_from_k ? 1 : 2) * G) * D) return (int)cudaErrorInvalidValue;
   const int vec = dtype == VX_DTYPE_F32 ? 4 : 8;
-  const bool aligned = (reinterpret_cast<uintptr_t>(qkv) & 15) == 0 &&
+  const bool aligned = (reinterpret_cast<uintptr_t>(qkv) & 15) == 0 && row_width % vec == 0 &&
                        (reinterpret_cast<uintptr_t>(k_cache) & 15) == 0 &&
                        (reinterpret_cast<uintptr_t>(v_cache) & 15) == 0;
   // The whole head rotates and a half is whole vectors (of angles too): pairs of chunks.
@@ -754,11 +759,11 @@ VX_API int vx_rope_cache_write(void* qkv, int dtype, const int* positions, const
     if (dtype == VX_DTYPE_F32)
       launch_pdl(rope_cache_write_pair_kernel<float>, dim3((int)blocks), dim3(block), 0, stream, (float*)qkv, positions,
                  cos_t, sin_t, slots, (float*)k_cache, (float*)v_cache, H, G, D, max_pos, num_slots, write_cache,
-                 num_tokens, status);
+                 num_tokens, row_width, v_from_k, status);
     else
       launch_pdl(rope_cache_write_pair_kernel<__nv_bfloat16>, dim3((int)blocks), dim3(block), 0, stream,
                  (__nv_bfloat16*)qkv, positions, cos_t, sin_t, slots, (__nv_bfloat16*)k_cache, (__nv_bfloat16*)v_cache,
-                 H, G, D, max_pos, num_slots, write_cache, num_tokens, status);
+                 H, G, D, max_pos, num_slots, write_cache, num_tokens, row_width, v_from_k, status);
     return (int)cudaGetLastError();
   }
   if (aligned && D % vec == 0 && (rot / 2) % vec == 0) {
@@ -767,12 +772,12 @@ VX_API int vx_rope_cache_write(void* qkv, int dtype, const int* positions, const
     if (dtype == VX_DTYPE_F32)
       launch_pdl(rope_cache_write_vec_kernel<float>, dim3(num_tokens), dim3(block), 0, stream,
                  (float*)qkv, positions, cos_t, sin_t, slots, (float*)k_cache, (float*)v_cache, H, G,
-                 D, rot, max_pos, num_slots, write_cache, status);
+                 D, rot, max_pos, num_slots, write_cache, row_width, v_from_k, status);
     else
       launch_pdl(rope_cache_write_vec_kernel<__nv_bfloat16>, dim3(num_tokens), dim3(block), 0,
                  stream, (__nv_bfloat16*)qkv, positions, cos_t, sin_t, slots,
                  (__nv_bfloat16*)k_cache, (__nv_bfloat16*)v_cache, H, G, D, rot, max_pos, num_slots,
-                 write_cache, status);
+                 write_cache, row_width, v_from_k, status);
     return (int)cudaGetLastError();
   }
   const int threads = D >= 128 ? 64 : 32;
@@ -780,11 +785,11 @@ VX_API int vx_rope_cache_write(void* qkv, int dtype, const int* positions, const
   if (dtype == VX_DTYPE_F32)
     launch_pdl(rope_cache_write_kernel<float>, dim3(grid), dim3(threads), 0, stream, 
         (float*)qkv, positions, cos_t, sin_t, slots, (float*)k_cache, (float*)v_cache, H, G, D,
-        rot, max_pos, num_slots, write_cache, status);
+        rot, max_pos, num_slots, write_cache, row_width, v_from_k, status);
   else
     launch_pdl(rope_cache_write_kernel<__nv_bfloat16>, dim3(grid), dim3(threads), 0, stream, 
         (__nv_bfloat16*)qkv, positions, cos_t, sin_t, slots, (__nv_bfloat16*)k_cache,
-        (__nv_bfloat16*)v_cache, H, G, D, rot, max_pos, num_slots, write_cache, status);
+        (__nv_bfloat16*)v_cache, H, G, D, rot, max_pos, num_slots, write_cache, row_width, v_from_k, status);
   return (int)cudaGetLastError();
 }
 

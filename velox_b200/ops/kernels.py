@@ -47,7 +47,7 @@ def core():
         ]
         lib.vx_rope_cache_write.argtypes = [
             _ptr, _c_int, _ptr, _ptr, _ptr, _ptr, _ptr, _ptr,
-            _c_int, _c_int, _c_int, _c_int, _c_int, _c_int, _c_ll, _c_int, _ptr, _ptr,
+            _c_int, _c_int, _c_int, _c_int, _c_int, _c_int, _c_ll, _c_int, _c_ll, _c_int, _ptr, _ptr,
         ]
         lib.vx_swiglu.argtypes = [_ptr, _ptr, _c_int, _c_int, _c_int, _ptr]
         lib.vx_gemm_f32.argtypes = [_ptr, _ptr, _ptr, _ptr, _c_int, _c_int, _c_int, _ptr]
@@ -656,15 +656,18 @@ def rope_cache_write(
     head_dim: int,
     rotary_dim: int,
     status: torch.Tensor,
+    values_from_keys: bool = False,
 ) -> None:
     """Rotate q in place; rotate k and write k, v to the paged cache at ``slots``.
 
     ``k_cache``/``v_cache`` None: rotate q only (a layer that reads another layer's cache).
+    ``values_from_keys``: the rows hold q | k only; a token's values are its keys as they stand in
+    the row (k is rotated on its way into the cache, never in the row).
     """
     _need(qkv, qkv.dtype, "qkv")
     _need(positions, torch.int32, "positions")
     _need(slots, torch.int32, "slots")
-    if qkv.shape[1] != (num_heads + 2 * num_kv_heads) * head_dim:
+    if qkv.shape[1] != (num_heads + (1 if values_from_keys else 2) * num_kv_heads) * head_dim:
         raise ValueError("qkv width does not match the head counts")
     write = k_cache is not None
     if write:
@@ -685,7 +688,8 @@ def rope_cache_write(
         core().vx_rope_cache_write(_p(qkv), _code(qkv.dtype), _p(positions), _p(cos), _p(sin),
                                    _p(slots), _p(k_cache), _p(v_cache), num_tokens, num_heads,
                                    num_kv_heads, head_dim, rotary_dim, max_pos, num_slots,
-                                   1 if write else 0, _p(status), _stream()),
+                                   1 if write else 0, qkv.stride(0), 1 if values_from_keys else 0, _p(status),
+                                   _stream()),
         "rope_cache_write",
     )
 

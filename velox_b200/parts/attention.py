@@ -76,6 +76,7 @@ class Attention(Mixer):
         self.row_scale = getattr(position, "row_scale", None)
         self.b_qkv = None
         self.b_qkv_lowp = None
+        self.values_from_keys = False
         if "qkv.weight" in weights:
             self.proj_width = self.qkv_width
             self.w_qkv = self.expect("qkv.weight", (self.qkv_width, self.hidden_size))
@@ -112,16 +113,24 @@ class Attention(Mixer):
         from_keys = bool(params.get("values_from_keys", False))
         if from_keys and vd != kd:
             raise ValueError(f"values_from_keys: value_dim={vd} must equal key_dim={kd}")
-        # Values that are the unrotated keys: the key rows stand a second time where the value rows
-        # would, so the value columns of the projection are the keys before the rotation.
+        # Values that are the unrotated keys: the projection has q and k rows only, and the kernel
+        # that rotates k into its page copies the row's k, as it stands, into the value page.
+        self.values_from_keys = from_keys
+        if from_keys:
+            if self.head_gate or not hasattr(self.position, "rotate_and_store") or getattr(
+                    self.position, "layout", None) != "half":
+                raise ValueError("values_from_keys goes with the rotary_half position part and no gate per head")
+            self.qkv_width = self.q_size + self.kv_size
         pieces = [padded_heads(self.expect("q.weight", (H * kd, E)), H, kd),
                   padded_heads(self.expect("k.weight", (G * kd, E)), G, kd)]
-        pieces.append(pieces[1] if from_keys else padded_heads(self.expect("v.weight", (G * vd, E)), G, vd))
+        if not from_keys:
+            pieces.append(padded_heads(self.expect("v.weight", (G * vd, E)), G, vd))
         bias = None
         if params.get("qkv_bias", False):
             bias = [padded_heads(self.expect("q.bias", (H * kd,)), H, kd),
                     padded_heads(self.expect("k.bias", (G * kd,)), G, kd)]
-            bias.append(bias[1] if from_keys else padded_heads(self.expect("v.bias", (G * vd,)), G, vd))
+            if not from_keys:
+                bias.append(padded_heads(self.expect("v.bias", (G * vd,)), G, vd))
         if self.head_gate:
             pieces.append(self.expect("gate.weight", (H, E)))
             if bias is not None:
@@ -167,14 +176,18 @@ class Attention(Mixer):
         # Projection, rotation and cache write in one kernel, where the position encoding
         # offers its tables and the kernel takes the shape (it says no otherwise).
         tables = None
-        if _FUSE_ROPE:
+        if _FUSE_ROPE and not self.values_from_keys:
             tables = getattr(self.position, "full_rotation_tables", lambda: None)()
         if tables is None or not qkv_rope_linear(
                 x, self.w_qkv, self.b_qkv, qkv, T, ctx.status, ctx.positions, tables[0], tables[1],
                 group.slot_mapping, k_cache, v_cache, self.num_heads, self.num_kv_heads):
             linear(x, self.w_qkv, self.b_qkv, qkv, T, self.b_qkv_lowp, status=ctx.status)
-            self.position.rotate_and_store(qkv, ctx, group.slot_mapping, k_cache, v_cache,
-                                           self.num_heads, self.num_kv_heads)
+            if self.values_from_keys:
+                self.position.rotate_and_store(qkv, ctx, group.slot_mapping, k_cache, v_cache,
+                                               self.num_heads, self.num_kv_heads, values_from_keys=True)
+            else:
+                self.position.rotate_and_store(qkv, ctx, group.slot_mapping, k_cache, v_cache,
+                                               self.num_heads, self.num_kv_heads)
 
         attn = ws.get(f"attention.out{self.q_size}", (ws.max_tokens, self.q_size), self.dtype)
         plan = ctx.attention_plan(cache.group, self.attention_signature())

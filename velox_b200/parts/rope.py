@@ -76,10 +76,12 @@ class RotaryHalf(PositionEncoding):
         self.cos = cos.to(torch.float32).to(device).contiguous()
         self.sin = sin.to(torch.float32).to(device).contiguous()
 
-    def rotate_and_store(self, qkv, ctx, slots, k_cache, v_cache, num_heads, num_kv_heads):
+    def rotate_and_store(self, qkv, ctx, slots, k_cache, v_cache, num_heads, num_kv_heads, values_from_keys=False):
+        """``values_from_keys``: the rows hold q | k; the values written to the cache are the keys
+        before the rotation."""
         kernels.rope_cache_write(
             qkv, ctx.positions, self.cos, self.sin, slots, k_cache, v_cache, ctx.num_tokens,
-            num_heads, num_kv_heads, self.head_dim, self.rotary_dim, ctx.status,
+            num_heads, num_kv_heads, self.head_dim, self.rotary_dim, ctx.status, values_from_keys=values_from_keys,
         )
 
     def full_rotation_tables(self):
