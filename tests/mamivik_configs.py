@@ -82,11 +82,11 @@ WIDE = config(256, 500, 5, [
     layer("latent_attention", latent(4, 32, 64, 48, 192, 96, 0.12, 65, 500.0), dense(128)),
 ], eps=2e-5)
 
-# Head sizes between the common ones, one tap (no convolution state), four taps elsewhere would
-# not fit one model: this one has one tap; three heads per KV head; a state head of 48.
+# Head sizes between the common ones, one tap (no convolution state); three heads per KV head; a
+# state head of 48; both mixers' windows are equal, so they share a cache group.
 MID = config(192, 700, 1, [
     layer("parallel", parallel(left(6, 2, 72, 0.12, 100, 300000.0, 24), 2, 48, 1.5, 0.5), dense(320)),
-    layer("latent_attention", latent(6, 40, 24, 56, 88, 64, 0.13, 90, 20000.0), dense(200)),
+    layer("latent_attention", latent(6, 40, 24, 56, 88, 64, 0.13, 100, 20000.0), dense(200)),
 ], eps=1e-6)
 
 # Four taps with prompts shorter than the taps; only parallel layers.
@@ -95,10 +95,19 @@ TAPS = config(48, 90, 4, [
     layer("parallel", parallel(left(4, 1, 8, 0.4, 3, 100.0, 2), 1, 16, 1.1, 0.9), None),
 ], eps=1e-5)
 
-ALL = {"small": SMALL, "odd": ODD, "wide": WIDE, "mid": MID, "taps": TAPS}
+# Latents wider than the attention kernels' widest cached row: these layers run with keys and
+# values expanded per head.  One of them stretches its slow pairs, one has a value size above its
+# query size.
+BROAD = config(72, 150, 3, [
+    layer("latent_attention", latent(2, 16, 8, 24, 264, 20, 0.2, 11, 300.0, (2.0, 32, 8.0, 1.0)), dense(48)),
+    layer("parallel", parallel(left(2, 1, 16, 0.3, 20, 100.0, 8), 1, 16, 1.0, 1.0), None),
+    layer("latent_attention", latent(3, 8, 16, 40, 300, 44, 0.25, 1000, 5000.0), dense(40)),
+], eps=1e-5)
+
+ALL = {"small": SMALL, "odd": ODD, "wide": WIDE, "mid": MID, "taps": TAPS, "broad": BROAD}
 
 # The inner size of the decay's two small matrices is a tensor shape, not a configuration key.
-DECAY_RANKS = {"small": 8, "odd": 5, "wide": 16, "mid": 24, "taps": 3}
+DECAY_RANKS = {"small": 8, "odd": 5, "wide": 16, "mid": 24, "taps": 3, "broad": 8}
 
 
 def build_spec(cfg: Dict[str, Any], decay_rank: Optional[int] = None):

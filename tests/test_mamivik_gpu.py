@@ -325,6 +325,7 @@ CASES = {
     "wide": (mc.WIDE, 64, (130, 3, 65, 300, 64), 2.5),
     "mid": (mc.MID, 16, (40, 2, 101, 230, 91), 2.0),
     "taps": (mc.TAPS, 8, (2, 3, 1, 50, 24), 2.0),
+    "broad": (mc.BROAD, 16, (7, 1, 40, 90, 18), 2.0),
 }
 
 

@@ -29,6 +29,14 @@ whose exponential joins the softmax denominator (weight ``sink``).  ``gate`` "el
 is ``sigmoid(W_g x)`` over all ``heads * value_dim`` outputs, not one number per head.  The
 position part decides which dims are a rotating pair (``layout``: neighbours, or dim i with dim
 i + pairs).
+
+A cached row of ``kv_rank + rot_dim`` values must fit the attention kernels' widest row (256).  A
+wider latent (with ``query_rank``) runs in the expanded form instead (``form``: "absorbed",
+"expanded", or "auto", which picks by that width): keys ``[k_rot | W_uk[h] c]`` and values
+``W_uv[h] c`` are made per head by one projection of ``[normed query latent | k_rot | c]`` whose
+matrix holds W_uq, W_uk, W_uv and an identity for the shared part (rotated dims first in every
+head, so the engine's rotate-and-store kernel takes them), cached per head, and attended to as
+ordinary heads; the pages then cost ``2 * heads * head_dim`` values a token instead of one row.
 """
 from __future__ import annotations
 
@@ -70,10 +78,14 @@ class LatentAttention(Mixer):
         self.position = position
         # A cached row, padded to what the attention kernels take (a multiple of 16 up to 256).
         self.row_dim = -(-(self.kv_rank + self.rot_dim) // 16) * 16
-        if self.row_dim > 256:
+        form = params.get("form", "auto")
+        if form not in ("auto", "absorbed", "expanded"):
+            raise ValueError(f"latent attention: form is 'auto', 'absorbed' or 'expanded', not {form!r}")
+        self.expanded = form == "expanded" or (form == "auto" and self.row_dim > 256 and self.query_rank > 0)
+        if self.row_dim > 256 and not self.expanded:
             raise ValueError(
                 f"kv_rank + rot_dim = {self.kv_rank + self.rot_dim} is more than the attention kernels' "
-                "largest row of 256"
+                "largest row of 256 (the expanded form takes wider latents of layers with a query latent)"
             )
         H, q_head = self.num_heads, self.dim + self.rot_dim
         self.q_offset = self.side_rows
@@ -112,17 +124,109 @@ class LatentAttention(Mixer):
         self.w_uk_t = w_uk.view(H, self.dim, self.kv_rank).transpose(1, 2).contiguous()
         self.w_uv = self.expect("uv.weight", (H * self.value_dim, self.kv_rank)).view(H, self.value_dim, self.kv_rank)
         self.w_out = self.expect("out.weight", (self.hidden_size, H * self.value_dim))
-        kernels.attention_lib(self.row_dim)
+        if self.expanded:
+            self._build_expanded(w_uk)
+        kernels.attention_lib(self.head_dim if self.expanded else self.row_dim)
+
+    def _build_expanded(self, w_uk: torch.Tensor) -> None:
+        """The one matrix of the expanded form.  Its input columns are ``[normed query latent (padded) |
+        k_rot | c (padded)]``; its rows are, head by head, the queries ``[rotated | unrotated | 0]``,
+        then the keys ``[k_rot | W_uk[h] c | 0]`` (an identity copies the shared part into every head),
+        then the values ``[W_uv[h] c | 0]``, every head ``head_dim`` rows."""
+        if not (self.query_rank and self.own_latent and not self.side_rows):
+            raise ValueError("the expanded form of latent attention needs a query latent, a down projection of "
+                             "its own and no side rows")
+        H, D, R, V, rank = self.num_heads, self.dim, self.rot_dim, self.value_dim, self.kv_rank
+        self.head_dim = Dh = -(-max(D + R, V) // 16) * 16
+        if Dh > 256:
+            raise ValueError(f"heads of {max(D + R, V)} values are more than the attention kernels' largest of 256")
+        Cq = self.query_rank_padded
+        cols = -(-(Cq + R + rank) // 8) * 8
+        self.x_cols, self.x_rot_at, self.x_latent_at = cols, Cq, Cq + R
+        w_uq = self.w_uq.view(H, D + R, Cq)
+        big = w_uq.new_zeros(3 * H, Dh, cols)
+        big[:H, :R, :Cq] = w_uq[:, D:]
+        big[:H, R : R + D, :Cq] = w_uq[:, :D]
+        big[H : 2 * H, :R, Cq : Cq + R] = torch.eye(R, dtype=big.dtype, device=big.device)
+        big[H : 2 * H, R : R + D, Cq + R : Cq + R + rank] = w_uk.view(H, D, rank)
+        big[2 * H :, :V, Cq + R : Cq + R + rank] = self.w_uv
+        self.w_heads = big.reshape(3 * H * Dh, cols).contiguous()
+        # The heads' first ``value_dim`` values, gated: a per-head product with an identity.
+        pick = w_uq.new_zeros(H, V, Dh)
+        pick[:, :, :V] = torch.eye(V, dtype=pick.dtype, device=pick.device)
+        self.w_pick = pick.contiguous()
+        kernels.mixers()
 
     def cache_needs(self) -> CacheNeeds:
+        if self.expanded:
+            return CacheNeeds(paged=PagedCacheSpec(self.num_heads, self.head_dim, self.window))
         return CacheNeeds(paged=PagedCacheSpec(1, self.row_dim, self.window, values_in_keys=True))
 
     def attention_signature(self):
-        base = (1, self.num_heads, self.window, self.row_dim)
+        base = ((self.num_heads, 1, self.window, self.head_dim) if self.expanded
+                else (1, self.num_heads, self.window, self.row_dim))
         # A sink comes in where split key ranges are merged: such rows always take that way.
         return base + (0, True) if self.sink is not None else base
 
+    def _attend(self, queries, attn, cache, ctx, kv_heads, head_dim):
+        group = ctx.groups[cache.group]
+        H = self.num_heads
+        plan = ctx.attention_plan(cache.group, self.attention_signature())
+        for kind, items, count in plan.launches:
+            kernels.attention(
+                kind, queries, attn, cache.k, cache.v, group.block_tables, ctx.q_start, ctx.q_len,
+                ctx.kv_len, items, count, plan.partial_o, plan.partial_lse, H, kv_heads, head_dim, self.window,
+                self.softmax_scale, merge_items=plan.merge_items, split_counters=plan.split_counters,
+                status=ctx.status,
+                cluster=(plan.cluster if kind == kernels.ATTN_BF16_NARROW else
+                         getattr(plan, "tc_ctas_per_sm", 1) if kind == kernels.ATTN_BF16_TC else 1),
+                layout_checked=getattr(plan, "checked", False),
+            )
+        if hasattr(plan, "checked"):
+            plan.checked = True
+        if plan.num_merges and plan.split_counters is None:
+            kernels.attention_merge(
+                attn, ctx.q_start, plan.merge_items, plan.num_merges, plan.partial_o, plan.partial_lse,
+                H, kv_heads, head_dim, max_rows=plan.merge_rows, sinks=self.sink,
+            )
+
+    def _forward_expanded(self, x, ctx, cache):
+        T = ctx.num_tokens
+        ws = ctx.workspace
+        H, Dh, R, rank = self.num_heads, self.head_dim, self.rot_dim, self.kv_rank
+        proj = ws.get(f"latent.proj{self.in_width}", (ws.max_tokens, self.in_width), self.dtype)
+        linear(x, self.w_in, None, proj, T, status=ctx.status)
+        # [normed query latent | k_rot | normed latent], each norm filling its padding with zeros.
+        both = ws.get(f"latent.both{self.x_cols}", (ws.max_tokens, self.x_cols), self.dtype)
+        kernels.rms_rows(proj[:, self.q_offset : self.q_offset + self.query_rank], self.query_norm, self.eps,
+                         both[:, : self.x_rot_at], T)
+        at = self.latent_offset
+        kernels.act_rows(proj[:, at + rank : at + rank + R], both[:, self.x_rot_at : self.x_latent_at], T,
+                         kernels.ACT_NONE)
+        kernels.rms_rows(proj[:, at : at + rank], self.latent_norm, self.eps, both[:, self.x_latent_at :], T)
+        qkv = ws.get(f"latent.heads_qkv{3 * H * Dh}", (ws.max_tokens, 3 * H * Dh), self.dtype)
+        linear(both, self.w_heads, None, qkv, T, status=ctx.status)
+        group = ctx.groups[cache.group]
+        rotating = 2 * self.position.pairs
+        if self.half_layout:
+            kernels.rope_cache_write(qkv, ctx.positions, self.position.cos, self.position.sin, group.slot_mapping,
+                                     cache.k, cache.v, T, H, H, Dh, rotating, ctx.status)
+        else:
+            kernels.pair_rope_cache_write(qkv, ctx.positions, self.position.cos, self.position.sin, group.slot_mapping,
+                                          cache.k, cache.v, T, H, H, Dh, rotating, ctx.status)
+        attn = ws.get(f"latent.attn{H * Dh}", (ws.max_tokens, H * Dh), self.dtype)
+        self._attend(qkv, attn, cache, ctx, H, Dh)
+        heads_out = ws.get(f"latent.heads{H * self.value_dim}", (ws.max_tokens, H * self.value_dim), self.dtype)
+        kernels.headwise_linear(attn, 0, Dh, self.w_pick, heads_out, 0, self.value_dim, T,
+                                gate=proj if self.gated else None, gate_offset=self.gate_offset,
+                                gate_each=self.gate_each)
+        out = ws.get("mixer.out", (ws.max_tokens, self.hidden_size), self.dtype)
+        linear(heads_out, self.w_out, None, out, T, status=ctx.status)
+        return out
+
     def forward(self, x, ctx, cache):
+        if self.expanded:
+            return self._forward_expanded(x, ctx, cache)
         T = ctx.num_tokens
         ws = ctx.workspace
         H, Dp = self.num_heads, self.row_dim
@@ -155,24 +259,7 @@ class LatentAttention(Mixer):
         kernels.headwise_linear(q_rows, q_offset, self.dim + self.rot_dim, self.w_uk_t, queries, 0, Dp, T)
 
         attn = ws.get(f"latent.attn{H * Dp}", (ws.max_tokens, H * Dp), self.dtype)
-        plan = ctx.attention_plan(cache.group, self.attention_signature())
-        for kind, items, count in plan.launches:
-            kernels.attention(
-                kind, queries, attn, cache.k, cache.k, group.block_tables, ctx.q_start, ctx.q_len,
-                ctx.kv_len, items, count, plan.partial_o, plan.partial_lse, H, 1, Dp, self.window,
-                self.softmax_scale, merge_items=plan.merge_items, split_counters=plan.split_counters,
-                status=ctx.status,
-                cluster=(plan.cluster if kind == kernels.ATTN_BF16_NARROW else
-                         getattr(plan, "tc_ctas_per_sm", 1) if kind == kernels.ATTN_BF16_TC else 1),
-                layout_checked=getattr(plan, "checked", False),
-            )
-        if hasattr(plan, "checked"):
-            plan.checked = True
-        if plan.num_merges and plan.split_counters is None:
-            kernels.attention_merge(
-                attn, ctx.q_start, plan.merge_items, plan.num_merges, plan.partial_o, plan.partial_lse,
-                H, 1, Dp, max_rows=plan.merge_rows, sinks=self.sink,
-            )
+        self._attend(queries, attn, cache, ctx, 1, Dp)
 
         heads_out = ws.get(f"latent.heads{H * self.value_dim}", (ws.max_tokens, H * self.value_dim), self.dtype)
         kernels.headwise_linear(attn, 0, Dp, self.w_uv, heads_out, 0, self.value_dim, T,
