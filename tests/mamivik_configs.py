@@ -27,9 +27,9 @@ def rot(base, dims, scaling=None) -> Dict[str, Any]:
     return out
 
 
-def latent(heads, dim, rot_dim, vdim, kv_rank, q_rank, scale, window, base, scaling=None) -> Dict[str, Any]:
+def latent(heads, dim, rot_dim, vdim, kv_rank, q_rank, scale, window, base, scaling=None, dims=None) -> Dict[str, Any]:
     return {"heads": heads, "dim": dim, "rot_dim": rot_dim, "vdim": vdim, "kv_rank": kv_rank, "q_rank": q_rank,
-            "scale": scale, "mask": {"size": window}, "rot": rot(base, rot_dim, scaling)}
+            "scale": scale, "mask": {"size": window}, "rot": rot(base, rot_dim if dims is None else dims, scaling)}
 
 
 def left(heads, kv_heads, dim, scale, window, base, dims, scaling=None) -> Dict[str, Any]:
@@ -83,10 +83,11 @@ WIDE = config(256, 500, 5, [
 ], eps=2e-5)
 
 # Head sizes between the common ones, one tap (no convolution state); three heads per KV head; a
-# state head of 48; both mixers' windows are equal, so they share a cache group.
+# state head of 48; both mixers' windows are equal, so they share a cache group; only 16 of the latent
+# layer's 24 rotated dims turn.
 MID = config(192, 700, 1, [
     layer("parallel", parallel(left(6, 2, 72, 0.12, 100, 300000.0, 24), 2, 48, 1.5, 0.5), dense(320)),
-    layer("latent_attention", latent(6, 40, 24, 56, 88, 64, 0.13, 100, 20000.0), dense(200)),
+    layer("latent_attention", latent(6, 40, 24, 56, 88, 64, 0.13, 100, 20000.0, dims=16), dense(200)),
 ], eps=1e-6)
 
 # Four taps with prompts shorter than the taps; only parallel layers.

@@ -47,7 +47,7 @@ def test_what_the_configuration_refuses():
     broken(lambda c: c["layers"][0]["mixer"]["left"]["rot"].update(dims=7))
     broken(lambda c: c["layers"][0]["mixer"]["left"]["rot"].update(dims=32))
     broken(lambda c: c["layers"][0]["mixer"].pop("left_scale"))
-    broken(lambda c: c["layers"][1]["mixer"]["rot"].update(dims=4))            # the whole rotated part turns
+    broken(lambda c: c["layers"][1]["mixer"]["rot"].update(dims=10))           # more than the rotated part has
     broken(lambda c: c["layers"][1]["mixer"]["rot"]["scaling"].update(factor=0.0))
     broken(lambda c: c["layers"][1]["mixer"].pop("q_rank"))
     broken(lambda c: c["layers"][1]["mixer"]["mask"].update(size=0))

@@ -875,7 +875,7 @@ class WindowedLatentConfig:
     """Latent attention over a sliding window: ``heads`` heads of ``dim`` unrotated and ``rot_dim``
     rotated query/key dims and ``vdim`` value dims over a cached latent of ``kv_rank`` values; the
     queries come through a normed latent of ``q_rank`` values; ``rot`` = (base, dims, scaling or
-    None) turns the rotated part in halves; a learned sink per head joins the softmax denominator
+    None) turns the first ``dims`` of the rotated part in halves; a learned sink per head joins the softmax denominator
     and the heads' outputs pass an element-wise gate."""
 
     heads: int
@@ -892,8 +892,6 @@ class WindowedLatentConfig:
     def parse(m: Mapping[str, Any], where: str) -> "WindowedLatentConfig":
         rot_dim = _count(m, "rot_dim", where)
         rot = _rotation(m, where, rot_dim, "rot_dim")
-        if rot[1] != rot_dim:
-            raise ConfigError(f"{where}.rot: dims={rot[1]} must equal rot_dim={rot_dim} (the whole rotated part turns)")
         window, _ = _window(m, where, keep_allowed=False)
         return WindowedLatentConfig(
             heads=_count(m, "heads", where), dim=_count(m, "dim", where), rot_dim=rot_dim, vdim=_count(m, "vdim", where),
