@@ -147,7 +147,8 @@ __global__ void norm_shift_kernel(const float* __restrict__ resid, long long res
 // of the tile's rows and of the taps - 1 rows before them, then all threads write the tile's
 // outputs.  The block of a portion's first tile is the only one that reads the state row, and it
 // writes the portion's last taps - 1 values of h there when its outputs are done (entries of a
-// portion shorter than that move up).  Rows of no request (padding of a rounded step, behind the
+// portion shorter than that move up).  A portion of one token (decode) moves its channels' entries up
+// and appends its h in the same loop that writes its output: a thread holds them all.  Rows of no request (padding of a rounded step, behind the
 // sequences' rows) come in tiles of rows without history.  The taps are given transposed, [taps x
 // width], so that a tap of neighbouring channels is one load.
 constexpr int NC_MAX_TAPS = 8;
@@ -235,6 +236,10 @@ norm_conv_kernel(const float* __restrict__ resid, long long resid_stride, int wi
   }
   __syncthreads();
   const float* old_state = (seq >= 0 && taps > 1) ? state + (size_t)seq_slots[seq] * state_stride : nullptr;
+  // One token of a request: its inputs from before are the whole state row, and the row after the
+  // step is those entries moved up by one with the token's h behind them.
+  const bool single = seq >= 0 && count == 1 && taps > 1;
+  float* own_state = single ? state + (size_t)seq_slots[seq] * state_stride : nullptr;
   if (vec && (reinterpret_cast<uintptr_t>(old_state) & 15) == 0 && state_stride % 4 == 0 &&
       (reinterpret_cast<uintptr_t>(cw_t) & 15) == 0 && (reinterpret_cast<uintptr_t>(w) & 15) == 0) {
     // Four channels a thread: every load of a pack's taps is under way before the first product.
@@ -278,6 +283,12 @@ norm_conv_kernel(const float* __restrict__ resid, long long resid_stride, int wi
       T* dst = out + (size_t)(first + row) * width + i;
 #pragma unroll
       for (int c = 0; c < 4; ++c) dst[c] = from_float<T>(result[c]);
+      if (single) {
+#pragma unroll
+        for (int j = 1; j < NC_MAX_TAPS; ++j)
+          if (j < taps - 1) *reinterpret_cast<float4*>(own_state + (size_t)(j - 1) * width + i) = x[j];
+        *reinterpret_cast<float4*>(own_state + (size_t)(taps - 2) * width + i) = make_float4(h[0], h[1], h[2], h[3]);
+      }
     }
   } else {
     for (int idx = threadIdx.x; idx < rows * width; idx += blockDim.x) {
@@ -296,9 +307,13 @@ norm_conv_kernel(const float* __restrict__ resid, long long resid_stride, int wi
       }
       // h is now the row's own value (j = taps - 1).
       out[(size_t)(first + row) * width + i] = from_float<T>(h + acc);
+      if (single) {
+        for (int e = 0; e + 1 < taps - 1; ++e) own_state[(size_t)e * width + i] = own_state[(size_t)(e + 1) * width + i];
+        own_state[(size_t)(taps - 2) * width + i] = h;
+      }
     }
   }
-  if (seq < 0 || tile != 0 || taps < 2) return;
+  if (seq < 0 || tile != 0 || taps < 2 || single) return;
   // New state: entry e is h of portion index count - (taps - 1) + e; a negative index is the old
   // entry count + e, which lies above e, and a thread moves its own channels in rising e.
   __syncthreads();
