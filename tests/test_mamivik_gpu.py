@@ -161,6 +161,60 @@ def test_delta_rule_scan_in_portions(dtype, heads, dim):
     assert bool((state[1] == 3.0).all())
 
 
+@pytest.mark.parametrize("heads,dim", [(2, 16), (1, 64), (3, 24)])
+def test_delta_rule_scan_in_chunks(heads, dim):
+    """Steps of 512 tokens and more run in chunks of 256 tokens side by side: a portion of three
+    chunks and a bit, one of exactly two, a short one and a single token in one step, from states
+    that are not zero; then each sequence goes on, so that the kept states are used."""
+    from velox_b200.ops import kernels
+
+    gen = torch.Generator().manual_seed(heads + dim)
+    inner = heads * dim
+    first, second = [800, 512, 37, 1], [3, 600, 1, 20]
+    decay, key_eps = math.exp(-0.5), 1e-6
+    w0 = (1.5 * torch.randn(inner, generator=gen)).float()
+    ab = (1.5 * torch.randn(inner, generator=gen)).float()
+    seqs = len(first)
+    proj = [torch.randn(a + b, 4 * inner, generator=gen) for a, b in zip(first, second)]
+    logit = [2.0 * torch.randn(a + b, inner, generator=gen) for a, b in zip(first, second)]
+    start = [0.3 * torch.randn(heads, dim, dim, generator=gen) for _ in range(seqs)]      # [head][row][column]
+    want = []
+    for p, l, s0 in zip(proj, logit, start):
+        pd, ld = p.double().numpy(), l.double().numpy()
+        r, k, v, a = (pd[:, i * inner : (i + 1) * inner].reshape(-1, heads, dim) for i in range(4))
+        w = np.exp(-decay * plain.sigmoid(ld + w0.double().numpy())).reshape(-1, heads, dim)
+        a = plain.sigmoid(a.reshape(-1, inner) + ab.double().numpy()).reshape(-1, heads, dim)
+        outs = [plain.delta_rule_states(r[:, h], k[:, h], v[:, h], w[:, h], a[:, h], S=s0[h].double().numpy())[0]
+                for h in range(heads)]
+        want.append(np.stack(outs, axis=1).reshape(-1, inner))
+    state = torch.zeros(seqs + 1, inner * dim).cuda()
+    for s in range(seqs):
+        state[s] = start[s].transpose(1, 2).reshape(-1).cuda()                             # stored [head][column][row]
+    got = [np.zeros((a + b, inner)) for a, b in zip(first, second)]
+    done = [0] * seqs
+    for sizes in (first, second):
+        total = sum(sizes)
+        rows = torch.cat([proj[s][done[s] : done[s] + n] for s, n in enumerate(sizes)]).cuda()
+        lg = torch.cat([logit[s][done[s] : done[s] + n] for s, n in enumerate(sizes)]).cuda()
+        out = torch.zeros(total, inner).cuda()
+        q_start, q_len, seq_slots = step_arrays(sizes, list(range(seqs)))
+        packed = torch.zeros(total, kernels.delta_rule_packed_width(heads, dim, dim)).cuda()
+        scratch = torch.zeros(kernels.delta_rule_chunk_scratch(total, seqs, heads, dim, dim)).cuda()
+        status = torch.zeros(4, dtype=torch.int32).cuda()
+        kernels.delta_rule_scan(rows[:, :inner], rows[:, inner : 2 * inner], rows[:, 2 * inner : 3 * inner],
+                                rows[:, 3 * inner : 4 * inner], lg, w0.cuda(), ab.cuda(), decay, key_eps, state, out,
+                                heads, dim, dim, q_start, q_len, seq_slots, seqs, total, packed, status,
+                                chunk_scratch=scratch)
+        assert int(status[0]) == 0
+        at = 0
+        for s, n in enumerate(sizes):
+            got[s][done[s] : done[s] + n] = out[at : at + n].double().cpu().numpy()
+            done[s] += n
+            at += n
+    for s in range(seqs):
+        close(torch.from_numpy(got[s]), want[s], "float32", f"sequence {s}", scale=float(np.abs(want[s]).max()), f32=5e-5)
+
+
 @pytest.mark.parametrize("dtype", list(DTYPES))
 @pytest.mark.parametrize("T,heads,dim", [(1, 2, 16), (19, 3, 24), (300, 4, 64)])
 def test_delta_rule_output_norm_and_gate(dtype, T, heads, dim):

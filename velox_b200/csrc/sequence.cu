@@ -566,8 +566,24 @@ __global__ void ssd_combine_kernel(float* __restrict__ state, long long state_st
 // each with its mbarrier, so the next tile arrives while this one is worked through.  The state is
 // stored [head][column][row]: a thread's rows are contiguous.  Every sum has a fixed order, so a
 // token's result does not depend on how the sequence was cut into steps.
+//
+// Long portions (a step of at least two chunks of DR_CHUNK tokens) run in three launches, chunks
+// side by side.  A token's transition, diag(w) - (a u) u^T, is not diagonal, so a chunk's
+// transition P is a dense Dk x Dk matrix: its columns are the images of the unit vectors, that is,
+// Dk more columns of state that start as the identity and see no k v^T.  Pass A (mode 1) runs every
+// chunk but a portion's last from zero over Dv + Dk columns and keeps the result Z | P; the fold
+// kernel makes the chunks' starting states in order, S_0 the state, S_(c+1) = P_c S_c + Z_c; pass B (mode 2) runs
+// every chunk again from its start and writes the outputs, its last chunk the state.  A portion of
+// one chunk skips pass A and the fold.  In this form a token's result depends, within float32
+// rounding, on where its chunk began.
 constexpr int DR_KP_SMALL = 4, DR_KP_LARGE = 16, DR_SMALL_MAX_DK = 128;
 constexpr size_t DR_MIN_SMEM = 116 * 1024;
+constexpr int DR_CHUNK = 256;
+
+// Where chunk `chunk` of sequence `seq` keeps its Z | P and its starting state: chunks of one
+// sequence begin DR_CHUNK rows apart, and later sequences begin at later rows, so the number is
+// taken by nobody else; it is below ceil(tokens / DR_CHUNK) + sequences.
+__device__ __forceinline__ int dr_chunk_slot(int seq, int first_row) { return first_row / DR_CHUNK + seq; }
 
 template <typename T>
 __global__ void __launch_bounds__(256)
@@ -616,25 +632,48 @@ __global__ void delta_rule_scan_kernel(const float* __restrict__ packed, long lo
                                        float* __restrict__ state, long long state_stride, float* __restrict__ out,
                                        long long out_stride, int Dk, int Dv, int Dvp, int CB, int TT,
                                        const int* __restrict__ q_start, const int* __restrict__ q_len,
-                                       const int* __restrict__ seq_slots, int* status) {
+                                       const int* __restrict__ seq_slots, int mode, int max_chunks, int heads,
+                                       float* __restrict__ chunk_results, float* __restrict__ chunk_starts,
+                                       int* status) {
   extern __shared__ __align__(16) float dr_smem[];
   __shared__ __align__(8) unsigned long long dr_bars[2];
   // The successor is let in when the scan is over: its blocks would share the few busy SMs'
   // issue slots with a kernel whose every token waits for the token before it.
-  const int seq = blockIdx.x, h = blockIdx.y, tile = blockIdx.z;
-  const int n = q_len[seq];
-  if (n <= 0) {
+  const int seq = blockIdx.x / max_chunks, chunk = blockIdx.x - seq * max_chunks;
+  const int h = blockIdx.y, tile = blockIdx.z;
+  const int n_all = q_len[seq];
+  const int chunks = mode == 0 ? 1 : (n_all + DR_CHUNK - 1) / DR_CHUNK;
+  // Pass A has nothing to do for a portion's last chunk (nobody starts behind it).
+  if (n_all <= 0 || chunk >= chunks || (mode == 1 && chunk == chunks - 1)) {
     allow_dependents();
     return;
   }
-  const int t_first = q_start[seq];
+  const int t_first = q_start[seq] + (mode == 0 ? 0 : chunk * DR_CHUNK);
+  const int n = mode == 0 ? n_all : min(DR_CHUNK, n_all - chunk * DR_CHUNK);
   constexpr int KD = RL * DR_KP;
   constexpr int vec = 5 * KD;                   // floats of a token's vectors over the key channels
   const int token_floats = vec + Dvp;
   const int p = threadIdx.x % RL, c = threadIdx.x / RL;
   const int col = tile * CB + c;
-  const bool live = col < Dv;
-  float* mine = state + (size_t)seq_slots[seq] * state_stride + ((size_t)h * Dv + (live ? col : 0)) * Dk;
+  const int num_cols = mode == 1 ? Dv + Dk : Dv;  // pass A: Dk more columns carry the chunk's transition
+  const bool live = col < num_cols;
+  const bool value_col = col < Dv;
+  const size_t safe_col = live ? col : 0;
+  // Where this thread's rows come from and go to.
+  float* state_rows = state + (size_t)seq_slots[seq] * state_stride + ((size_t)h * Dv + (value_col ? col : 0)) * Dk;
+  const int slot_here = dr_chunk_slot(seq, t_first);
+  const float* from = state_rows;
+  float* mine = state_rows;
+  if (mode == 1) {
+    from = nullptr;
+    mine = chunk_results + (((size_t)slot_here * heads + h) * (size_t)(Dv + Dk) + safe_col) * Dk;
+  } else if (mode == 2 && chunks > 1) {
+    // Every chunk of a cut portion starts from the fold kernel's copy, the first one too: the block
+    // of the last chunk writes the state row, and nothing says that it does so after the first
+    // chunk's block has read it.
+    from = chunk_starts + (((size_t)slot_here * heads + h) * (size_t)Dv + safe_col) * Dk;
+    if (chunk < chunks - 1) mine = nullptr;  // only a portion's last chunk leaves the state behind
+  }
   const uint32_t bar0 = smem_u32(&dr_bars[0]), bar1 = smem_u32(&dr_bars[1]);
   if (threadIdx.x == 0) {
     mbar_init(bar0, 1);
@@ -663,7 +702,8 @@ __global__ void delta_rule_scan_kernel(const float* __restrict__ packed, long lo
 #pragma unroll
   for (int q = 0; q < DR_KP; ++q) {
     const int row = p * DR_KP + q;
-    S[q] = (live && row < Dk) ? mine[row] : 0.f;
+    if (from != nullptr) S[q] = (live && row < Dk) ? from[row] : 0.f;
+    else S[q] = (live && !value_col && row == col - Dv) ? 1.f : 0.f;  // zero, or a column of the identity
   }
   // One pass over the rows per token makes both sums that read the state as it is before the
   // token's update: u_t^T S for this token and S^T r for the token before (whose update is the last
@@ -711,8 +751,8 @@ __global__ void delta_rule_scan_kernel(const float* __restrict__ packed, long lo
           o += __shfl_xor_sync(0xffffffffu, o, off);
         }
       }
-      if (pending && live && p == 0) out[(size_t)pending_row * out_stride + (size_t)h * Dv + col] = o;
-      const float vj = tok[vec - p * DR_KP + (live ? col : 0)];
+      if (pending && mode != 1 && live && p == 0) out[(size_t)pending_row * out_stride + (size_t)h * Dv + col] = o;
+      const float vj = value_col ? tok[vec - p * DR_KP + col] : 0.f;
 #pragma unroll
       for (int q = 0; q < DR_KP / 4; ++q) {
         const float4 w = w4[q], a = a4[q], k = k4[q], r = r4[q];
@@ -745,15 +785,89 @@ __global__ void delta_rule_scan_kernel(const float* __restrict__ packed, long lo
 #pragma unroll
     for (int off = 16; off > 0; off >>= 1)
       if (off < RL) o += __shfl_xor_sync(0xffffffffu, o, off);
-    if (pending && live && p == 0) out[(size_t)pending_row * out_stride + (size_t)h * Dv + col] = o;
+    if (pending && mode != 1 && live && p == 0) out[(size_t)pending_row * out_stride + (size_t)h * Dv + col] = o;
   }
   allow_dependents();
-  if (live) {
+  if (live && mine != nullptr) {
 #pragma unroll
     for (int q = 0; q < DR_KP; ++q) {
       const int row = p * DR_KP + q;
       if (row < Dk) mine[row] = S[q];
     }
+  }
+}
+
+// The chunks' starting states, in order: S_(c+1) = P_c S_c + Z_c with S_0 the sequence's state.  A
+// block takes some value columns of one head of one sequence and keeps them in shared memory;
+// thread (row k, column j) sums over the rows i of S in rising order, reading column i of P, which is
+// stored as a run of Dk floats.
+__global__ void delta_rule_fold_kernel(const float* __restrict__ state, long long state_stride,
+                                       const float* __restrict__ chunk_results, float* __restrict__ chunk_starts,
+                                       int Dk, int Dv, int CBF, int heads, const int* __restrict__ q_start,
+                                       const int* __restrict__ q_len, const int* __restrict__ seq_slots,
+                                       int stage_p) {
+  extern __shared__ __align__(16) float fold_smem[];  // two buffers [CBF][Dk], then (stage_p) P [Dk][Dk]
+  allow_dependents();
+  const int seq = blockIdx.x, h = blockIdx.y, col0 = blockIdx.z * CBF;
+  const int n_all = q_len[seq];
+  const int chunks = (n_all + DR_CHUNK - 1) / DR_CHUNK;
+  if (n_all <= 0 || chunks < 2) return;
+  const int cols = min(CBF, Dv - col0);
+  float* now = fold_smem;
+  float* next = fold_smem + (size_t)CBF * Dk;
+  grid_dependency_wait();
+  const float* start = state + (size_t)seq_slots[seq] * state_stride + ((size_t)h * Dv + col0) * Dk;
+  const int first_row = q_start[seq];
+  float* first_start = chunk_starts + (((size_t)dr_chunk_slot(seq, first_row) * heads + h) * (size_t)Dv + col0) * Dk;
+  for (int idx = threadIdx.x; idx < cols * Dk; idx += blockDim.x) {
+    now[idx] = start[idx];
+    first_start[idx] = start[idx];  // the first chunk's start is the state as the step found it
+  }
+  __syncthreads();
+  for (int chunk = 0; chunk + 1 < chunks; ++chunk) {
+    const size_t here = ((size_t)dr_chunk_slot(seq, first_row + chunk * DR_CHUNK) * heads + h) * (size_t)(Dv + Dk) * Dk;
+    const float* Z = chunk_results + here + (size_t)col0 * Dk;   // [column j][row k]
+    const float* P = chunk_results + here + (size_t)Dv * Dk;     // [column i][row k]; 16-byte aligned when Dk % 4 == 0
+    float* dst = chunk_starts +
+                 (((size_t)dr_chunk_slot(seq, first_row + (chunk + 1) * DR_CHUNK) * heads + h) * (size_t)Dv + col0) * Dk;
+    if (stage_p) {
+      // The chunk's transition into shared memory, every load under way at once.
+      float* staged = fold_smem + 2 * (size_t)CBF * Dk;
+      for (int idx = threadIdx.x * 4; idx < Dk * Dk; idx += blockDim.x * 4)
+        *reinterpret_cast<float4*>(staged + idx) = *reinterpret_cast<const float4*>(P + idx);
+      __syncthreads();
+      P = staged;
+    }
+    // Four outputs a thread at a time, so that the loads of P (global memory, one per row i) of
+    // several rows are under way together: a single output's sum would wait for each in turn.
+    for (int base = threadIdx.x; base < cols * Dk; base += 4 * blockDim.x) {
+      int j[4], k[4];
+      float acc[4];
+#pragma unroll
+      for (int o = 0; o < 4; ++o) {
+        const int idx = min(base + o * (int)blockDim.x, cols * Dk - 1);
+        j[o] = idx / Dk;
+        k[o] = idx - j[o] * Dk;
+        acc[o] = Z[idx];
+      }
+#pragma unroll 8
+      for (int i = 0; i < Dk; ++i) {
+#pragma unroll
+        for (int o = 0; o < 4; ++o) acc[o] = fmaf(P[(size_t)i * Dk + k[o]], now[j[o] * Dk + i], acc[o]);
+      }
+#pragma unroll
+      for (int o = 0; o < 4; ++o) {
+        const int idx = base + o * (int)blockDim.x;
+        if (idx < cols * Dk) {
+          next[idx] = acc[o];
+          dst[idx] = acc[o];
+        }
+      }
+    }
+    __syncthreads();
+    float* swap = now;
+    now = next;
+    next = swap;
   }
 }
 
@@ -1084,6 +1198,12 @@ static int dr_pow2_at_least(int v) {
   return p;
 }
 
+// Floats of scratch the chunked form wants for a step of up to `num_tokens` tokens of `num_seqs` sequences.
+VX_API long long vx_delta_rule_chunk_scratch(int num_tokens, int num_seqs, int heads, int Dk, int Dv) {
+  const long long slots = (num_tokens + DR_CHUNK - 1) / DR_CHUNK + num_seqs;
+  return slots * heads * ((long long)(Dv + Dk) * Dk + (long long)Dv * Dk);
+}
+
 // Floats of one token's packed row (all heads), or -1 for a key size beyond the lanes of a warp.
 static int dr_rows_per_lane(int Dk) { return Dk <= DR_SMALL_MAX_DK ? DR_KP_SMALL : DR_KP_LARGE; }
 
@@ -1097,7 +1217,8 @@ VX_API int vx_delta_rule_packed_width(int heads, int Dk, int Dv) {
 template <int KP, int RL>
 static int dr_launch_scan(const float* packed, long long head_stride, float* state, long long state_stride,
                           float* out, long long out_stride, int heads, int Dk, int Dv, int Dvp,
-                          const int* q_start, const int* q_len, const int* seq_slots, int num_seqs, int* status,
+                          const int* q_start, const int* q_len, const int* seq_slots, int num_seqs, int mode,
+                          int max_chunks, float* chunk_results, float* chunk_starts, int* status,
                           cudaStream_t stream) {
   constexpr int KD = RL * KP;
   // Columns a block: four warps' worth where the lanes allow, a whole number of warps at least.
@@ -1106,7 +1227,7 @@ static int dr_launch_scan(const float* packed, long long head_stride, float* sta
   if (CB < 1) CB = 1;
   const int TT = KD <= 64 ? 16 : (KD <= 128 ? 8 : 4);
   size_t smem = sizeof(float) * 2 * (size_t)TT * (5 * KD + Dvp);
-  const dim3 grid(num_seqs, heads, (Dv + CB - 1) / CB);
+  const dim3 grid(num_seqs * max_chunks, heads, ((mode == 1 ? Dv + Dk : Dv) + CB - 1) / CB);
   // Few blocks (a prompt's portion): each gets an SM of its own.  Many blocks (single tokens of
   // many sequences) share the SMs as they fit.
   static int num_sms = 0;
@@ -1116,13 +1237,16 @@ static int dr_launch_scan(const float* packed, long long head_stride, float* sta
     cudaDeviceGetAttribute(&num_sms, cudaDevAttrMultiProcessorCount, device);
   }
   if ((long long)grid.x * grid.y * grid.z <= num_sms && smem < DR_MIN_SMEM) smem = DR_MIN_SMEM;
+  // The kernel has a few bytes of static shared memory beside these: ask from a kilobyte below
+  // the default limit on.
   static size_t limit = 0;  // one per instantiation
-  if (smem > 48 * 1024 && smem > limit) {
+  if (smem + 1024 > 48 * 1024 && smem > limit) {
     cudaFuncSetAttribute(delta_rule_scan_kernel<KP, RL>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     limit = smem;
   }
   launch_pdl(delta_rule_scan_kernel<KP, RL>, grid, dim3(CB * RL), smem, stream, packed, head_stride, state,
-             state_stride, out, out_stride, Dk, Dv, Dvp, CB, TT, q_start, q_len, seq_slots, status);
+             state_stride, out, out_stride, Dk, Dv, Dvp, CB, TT, q_start, q_len, seq_slots, mode, max_chunks, heads,
+             chunk_results, chunk_starts, status);
   return (int)cudaGetLastError();
 }
 
@@ -1131,7 +1255,8 @@ VX_API int vx_delta_rule_scan(const void* r, const void* k, const void* v, const
                               float key_eps, float* packed, long long packed_rows, float* state, long long state_stride,
                               float* out,
                               long long out_stride, int heads, int Dk, int Dv, const int* q_start, const int* q_len,
-                              const int* seq_slots, int num_seqs, int num_tokens, int* status, cudaStream_t stream) {
+                              const int* seq_slots, int num_seqs, int num_tokens, float* chunk_scratch,
+                              long long chunk_scratch_floats, int* status, cudaStream_t stream) {
   if (num_seqs <= 0 || num_tokens <= 0) return 0;
   if (heads <= 0 || Dk <= 0 || Dv <= 0) return (int)cudaErrorInvalidValue;
   const int KP = dr_rows_per_lane(Dk);
@@ -1146,20 +1271,49 @@ VX_API int vx_delta_rule_scan(const void* r, const void* k, const void* v, const
                                 w0, a_bias, decay, key_eps, packed, packed_stride, heads, Dk, Dv, KD, Dvp, num_tokens));
   int code = (int)cudaGetLastError();
   if (code != 0) return code;
+  // Long steps run in chunks when the caller has brought the scratch for it.
+  const bool chunked = num_tokens >= 2 * DR_CHUNK && chunk_scratch != nullptr &&
+                       chunk_scratch_floats >= vx_delta_rule_chunk_scratch(num_tokens, num_seqs, heads, Dk, Dv);
+  const int max_chunks = chunked ? (num_tokens + DR_CHUNK - 1) / DR_CHUNK : 1;
+  const long long slots = (long long)max_chunks + num_seqs;
+  float* chunk_results = chunk_scratch;
+  float* chunk_starts = chunked ? chunk_scratch + slots * heads * (long long)(Dv + Dk) * Dk : nullptr;
+  auto scan = [&](int mode) -> int {
 #define VX_DR(KPV, RLV)                                                                                          \
   if (KP == KPV && RL == RLV)                                                                                    \
     return dr_launch_scan<KPV, RLV>(packed, packed_stride, state, state_stride, out, out_stride, heads, Dk, Dv, Dvp, \
-                                    q_start, q_len, seq_slots, num_seqs, status, stream)
-  VX_DR(DR_KP_SMALL, 1);
-  VX_DR(DR_KP_SMALL, 2);
-  VX_DR(DR_KP_SMALL, 4);
-  VX_DR(DR_KP_SMALL, 8);
-  VX_DR(DR_KP_SMALL, 16);
-  VX_DR(DR_KP_SMALL, 32);
-  VX_DR(DR_KP_LARGE, 16);
-  VX_DR(DR_KP_LARGE, 32);
+                                    q_start, q_len, seq_slots, num_seqs, mode, max_chunks, chunk_results,        \
+                                    chunk_starts, status, stream)
+    VX_DR(DR_KP_SMALL, 1);
+    VX_DR(DR_KP_SMALL, 2);
+    VX_DR(DR_KP_SMALL, 4);
+    VX_DR(DR_KP_SMALL, 8);
+    VX_DR(DR_KP_SMALL, 16);
+    VX_DR(DR_KP_SMALL, 32);
+    VX_DR(DR_KP_LARGE, 16);
+    VX_DR(DR_KP_LARGE, 32);
 #undef VX_DR
-  return -1;
+    return -1;
+  };
+  if (!chunked) return scan(0);
+  code = scan(1);
+  if (code != 0) return code;
+  const int CBF = Dk <= 128 ? 16 : 4;
+  size_t fold_smem = sizeof(float) * 2 * (size_t)CBF * Dk;
+  // The chunk's Dk x Dk transition beside them where it fits (and its rows are whole 16-byte packs).
+  const int stage_p = Dk % 4 == 0 && fold_smem + sizeof(float) * (size_t)Dk * Dk <= 96 * 1024;
+  if (stage_p) fold_smem += sizeof(float) * (size_t)Dk * Dk;
+  static size_t fold_limit = 0;
+  if (fold_smem > 47 * 1024 && fold_smem > fold_limit) {
+    cudaFuncSetAttribute(delta_rule_fold_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)fold_smem);
+    fold_limit = fold_smem;
+  }
+  launch_pdl(delta_rule_fold_kernel, dim3(num_seqs, heads, (Dv + CBF - 1) / CBF), dim3(256), fold_smem, stream,
+             (const float*)state, state_stride, (const float*)chunk_results, chunk_starts, Dk, Dv, CBF, heads, q_start,
+             q_len, seq_slots, stage_p);
+  code = (int)cudaGetLastError();
+  if (code != 0) return code;
+  return scan(2);
 }
 
 VX_API int vx_gated_group_norm(const float* y, long long y_stride, const void* z, int dtype, long long z_stride,

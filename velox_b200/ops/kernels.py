@@ -147,8 +147,10 @@ def mixers():
         ]
         lib.vx_delta_rule_scan.argtypes = [
             _ptr, _ptr, _ptr, _ptr, _c_int, _c_ll, _ptr, _c_ll, _ptr, _ptr, _c_f, _c_f, _ptr, _c_ll, _ptr, _c_ll, _ptr,
-            _c_ll, _c_int, _c_int, _c_int, _ptr, _ptr, _ptr, _c_int, _c_int, _ptr, _ptr,
+            _c_ll, _c_int, _c_int, _c_int, _ptr, _ptr, _ptr, _c_int, _c_int, _ptr, _c_ll, _ptr, _ptr,
         ]
+        lib.vx_delta_rule_chunk_scratch.argtypes = [_c_int, _c_int, _c_int, _c_int, _c_int]
+        lib.vx_delta_rule_chunk_scratch.restype = _c_ll
         lib.vx_delta_rule_packed_width.argtypes = [_c_int, _c_int, _c_int]
         lib.vx_delta_rule_packed_width.restype = _c_int
         lib.vx_dual_norm_mean.argtypes = [_ptr, _ptr, _c_int, _ptr, _ptr, _c_f, _c_f, _c_int, _ptr, _ptr, _c_int, _ptr]
@@ -1492,15 +1494,22 @@ def delta_rule_packed_width(heads: int, key_dim: int, value_dim: int) -> int:
     return width
 
 
+def delta_rule_chunk_scratch(num_tokens: int, num_seqs: int, heads: int, key_dim: int, value_dim: int) -> int:
+    """float32 values of scratch with which ``delta_rule_scan`` runs long steps in chunks side by side."""
+    return int(mixers().vx_delta_rule_chunk_scratch(num_tokens, num_seqs, heads, key_dim, value_dim))
+
+
 def delta_rule_scan(r, k, v, a, w, w0, a_bias, decay, key_eps, state, out, heads, key_dim, value_dim, q_start, q_len,
-                    seq_slots, num_seqs, num_tokens, packed, status) -> None:
+                    seq_slots, num_seqs, num_tokens, packed, status, chunk_scratch=None) -> None:
     """The generalized delta rule over each sequence's tokens (csrc/sequence.cu).  ``r``, ``k``,
     ``v``, ``a`` are column ranges of one projection buffer [tokens, *] (heads x key_dim, value_dim for
     v), ``w`` the decay's logits [tokens, heads * key_dim]; ``w0``, ``a_bias`` float32 [heads *
     key_dim]; ``state`` float32, a row per state slot holding [heads, value_dim, key_dim]; ``out``
     float32 [tokens, heads * value_dim]; ``packed`` float32 scratch [at least tokens,
     delta_rule_packed_width(...)]: the tokens' vectors as the scan reads them (the kernels lay it
-    out head by head)."""
+    out head by head).  ``chunk_scratch`` (float32, ``delta_rule_chunk_scratch`` values for the step's
+    tokens and sequences at least): steps of 512 tokens and more then run in chunks of 256 tokens side
+    by side; a token's result then depends, within float32 rounding, on where its chunk began."""
     stride = _pitched(r, "r")
     if _pitched(k, "k") != stride or _pitched(v, "v") != stride or _pitched(a, "a") != stride:
         raise ValueError("delta_rule_scan: r, k, v and a are columns of one buffer")
@@ -1510,6 +1519,8 @@ def delta_rule_scan(r, k, v, a, w, w0, a_bias, decay, key_eps, state, out, heads
     _need(a_bias, torch.float32, "a_bias")
     _need(packed, torch.float32, "packed")
     _need(status, torch.int32, "status")
+    if chunk_scratch is not None:
+        _need(chunk_scratch, torch.float32, "chunk_scratch")
     if state.shape[1] < heads * key_dim * value_dim or state.stride(1) != 1:
         raise ValueError("delta_rule_scan: the state row is too small")
     if packed.shape[0] < num_tokens or packed.shape[1] != delta_rule_packed_width(heads, key_dim, value_dim):
@@ -1518,7 +1529,8 @@ def delta_rule_scan(r, k, v, a, w, w0, a_bias, decay, key_eps, state, out, heads
         _p(r), _p(k), _p(v), _p(a), _code(r.dtype), stride, _p(w), _pitched(w, "w"), _p(w0), _p(a_bias),
         float(decay), float(key_eps), _p(packed), packed.shape[0], _p(state), state.stride(0), _p(out),
         _pitched(out, "out"), heads,
-        key_dim, value_dim, _p(q_start), _p(q_len), _p(seq_slots), num_seqs, num_tokens, _p(status), _stream())
+        key_dim, value_dim, _p(q_start), _p(q_len), _p(seq_slots), num_seqs, num_tokens, _p(chunk_scratch),
+        0 if chunk_scratch is None else chunk_scratch.numel(), _p(status), _stream())
     if code == -1:
         raise KernelError(f"delta_rule_scan refuses a key size of {key_dim} (at most 512)")
     _check(code, "delta_rule_scan")

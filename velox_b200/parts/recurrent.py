@@ -265,11 +265,16 @@ class DeltaRule(Mixer):
         y = ws.get(f"delta_rule.y{inner}", (ws.max_tokens, inner), torch.float32)
         width = kernels.delta_rule_packed_width(self.heads, self.dim, self.dim)
         packed = ws.get(f"delta_rule.packed{width}", (ws.max_tokens, width), torch.float32)
+        scratch = None
+        if T >= 512:
+            # Long steps: chunks of tokens side by side.
+            size = kernels.delta_rule_chunk_scratch(ws.max_tokens, cache.state.shape[0], self.heads, self.dim, self.dim)
+            scratch = ws.get(f"delta_rule.chunks{self.heads}_{self.dim}", (size,), torch.float32)
         kernels.delta_rule_scan(
             proj[:, :inner], proj[:, inner : 2 * inner], proj[:, 2 * inner : 3 * inner],
             proj[:, 4 * inner : 5 * inner], logits, self.decay_bias, self.removal_bias, self.decay_scale,
             self.key_eps, cache.state, y, self.heads, self.dim, self.dim, ctx.q_start, ctx.q_len, ctx.seq_slots,
-            ctx.num_seqs, T, packed, ctx.status)
+            ctx.num_seqs, T, packed, ctx.status, chunk_scratch=scratch)
         normed = ws.get(f"delta_rule.normed{inner}", (ws.max_tokens, inner), self.dtype)
         kernels.gated_group_norm(y, proj[:, 3 * inner : 4 * inner], self.norm_w, self.eps, self.heads, normed, T,
                                  gate_after=True)
