@@ -161,7 +161,7 @@ def test_delta_rule_scan_in_portions(dtype, heads, dim):
     assert bool((state[1] == 3.0).all())
 
 
-@pytest.mark.parametrize("heads,dim", [(2, 16), (1, 64), (3, 24)])
+@pytest.mark.parametrize("heads,dim", [(2, 16), (1, 64), (3, 24), (1, 136), (2, 10)])
 def test_delta_rule_scan_in_chunks(heads, dim):
     """Steps of 512 tokens and more run in chunks of 256 tokens side by side: a portion of three
     chunks and a bit, one of exactly two, a short one and a single token in one step, from states
