@@ -1,7 +1,7 @@
 """The Mamivik design in the engine against the plain implementation in ``plain_mamivik``.
 
 First each mechanism's kernels alone (the norm with the input convolution and its state rows in
-portions, the delta rule's scan in portions beside other sequences, its normed and gated output,
+portions, the delta rule's scan in portions beside other sequences and in chunks, its normed and gated output,
 the norm of a column range, the latent layer's rotation in halves and its gate per output, the
 scaled sum of two mixers, the tanh GELU as a gated activation, stretched rotation tables), then
 whole models through trace replay: whole prompts, the last tokens decoded one by one, portions

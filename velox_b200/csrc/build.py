@@ -1,9 +1,9 @@
 """Compiles the CUDA sources of this directory for sm_100a and loads them with ctypes.
 
 There are four libraries: ``core`` (row-wise kernels, sampling, GEMMs; one build),
-``attention`` (one build per head size, ``-DVX_HEAD_DIM=<D>``), ``mixers`` (recurrent mixers
-and expert feed-forwards; one build) and ``heads`` (token shift, differential attention's two
-ends, the clamped gated activation; one build), so a process compiles what its model needs and
+``attention`` (one build per head size, ``-DVX_HEAD_DIM=<D>``), ``mixers`` (recurrent mixers,
+the delta rule among them, and expert feed-forwards; one build) and ``heads`` (token shift, the
+input convolution, differential attention's two ends, the gated activations; one build), so a process compiles what its model needs and
 nothing else.  A build is keyed by a hash of its sources, flags and compiler
 version; it is made once and reused.  Builds go to ``velox_b200/_build`` inside the package when
 that is writable, else to ``$VELOX_B200_BUILD_DIR``, else to a per-user folder under the
