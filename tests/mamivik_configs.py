@@ -105,10 +105,19 @@ BROAD = config(72, 150, 3, [
     layer("latent_attention", latent(3, 8, 16, 40, 300, 44, 0.25, 1000, 5000.0), dense(40)),
 ], eps=1e-5)
 
-ALL = {"small": SMALL, "odd": ODD, "wide": WIDE, "mid": MID, "taps": TAPS, "broad": BROAD}
+# More query heads on one cached row or KV head than an attention tile has rows: a token's heads are
+# cut across tiles, in the layer whose rows the sink's merge finishes and in the one beside the
+# delta rule.
+MANY = config(80, 200, 2, [
+    layer("latent_attention", latent(20, 8, 8, 8, 24, 16, 0.3, 30, 100.0), dense(64)),
+    layer("parallel", parallel(left(18, 1, 16, 0.25, 25, 1000.0, 8), 2, 8, 1.0, 0.7), None),
+    layer("latent_attention", latent(17, 16, 4, 12, 40, 24, 0.25, 1000, 100.0, (2.0, 16, 4.0, 1.0)), dense(40)),
+], eps=1e-5)
+
+ALL = {"small": SMALL, "odd": ODD, "wide": WIDE, "mid": MID, "taps": TAPS, "broad": BROAD, "many": MANY}
 
 # The inner size of the decay's two small matrices is a tensor shape, not a configuration key.
-DECAY_RANKS = {"small": 8, "odd": 5, "wide": 16, "mid": 24, "taps": 3, "broad": 8}
+DECAY_RANKS = {"small": 8, "odd": 5, "wide": 16, "mid": 24, "taps": 3, "broad": 8, "many": 4}
 
 
 def build_spec(cfg: Dict[str, Any], decay_rank: Optional[int] = None):

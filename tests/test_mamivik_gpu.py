@@ -380,6 +380,7 @@ CASES = {
     "mid": (mc.MID, 16, (40, 2, 101, 230, 91), 2.0),
     "taps": (mc.TAPS, 8, (2, 3, 1, 50, 24), 2.0),
     "broad": (mc.BROAD, 16, (7, 1, 40, 90, 18), 2.0),
+    "many": (mc.MANY, 16, (12, 1, 70, 33, 5), 2.0),
 }
 
 
