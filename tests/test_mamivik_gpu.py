@@ -294,6 +294,50 @@ def test_latent_rows_and_queries_rotated_in_halves(dtype, H, dim, R, rank, scali
 
 
 @pytest.mark.parametrize("dtype", list(DTYPES))
+@pytest.mark.parametrize("H,G,D,rot", [(4, 2, 32, 16), (3, 3, 16, 16), (6, 2, 48, 4), (2, 1, 64, 64), (5, 1, 16, 0)])
+def test_values_written_from_the_unrotated_key_columns(dtype, H, G, D, rot):
+    """Rows of q | k only: q turns in place, k turns on its way into its page, and the value page gets
+    the row's k as it stands (all three forms of the kernel: scalar, 16 bytes at a time, pairs)."""
+    from velox_b200.ops import kernels
+
+    dt = DTYPES[dtype]
+    gen = torch.Generator().manual_seed(H * D + rot)
+    T, P, pages = 6, 4, 5
+    spec = {"base": 100.0, "dims": rot}
+    positions = torch.tensor([0, 1, 9, 30, 31, 5], dtype=torch.int32)
+    slots = torch.tensor([4, 5, 6, -1, 17, 8], dtype=torch.int32)
+    rows = torch.randn(T, (H + G) * D, generator=gen).to(dt)
+    cos = sin = None
+    if rot:
+        f, _ = plain.frequencies(spec)
+        angle = np.arange(40)[:, None] * f[None, :]
+        cos = torch.tensor(np.cos(angle), dtype=torch.float32).cuda()
+        sin = torch.tensor(np.sin(angle), dtype=torch.float32).cuda()
+    k_cache = torch.zeros(pages, P, G, D, dtype=dt).cuda()
+    v_cache = torch.zeros(pages, P, G, D, dtype=dt).cuda()
+    status = torch.zeros(4, dtype=torch.int32).cuda()
+    on_device = rows.clone().cuda()
+    kernels.rope_cache_write(on_device, positions.cuda(), cos, sin, slots.cuda(), k_cache, v_cache, T, H, G, D, rot,
+                             status, values_from_keys=True)
+    assert int(status[0]) == 0
+    rd = rows.double().numpy()
+    q, k = rd[:, : H * D].reshape(T, H, D), rd[:, H * D :].reshape(T, G, D)
+    q_want = plain.rotate_halves(q, spec, positions.numpy()) if rot else q
+    k_want = plain.rotate_halves(k, spec, positions.numpy()) if rot else k
+    close(on_device[:, : H * D].view(T, H, D), q_want, dtype, "q in place")
+    assert torch.equal(on_device[:, H * D :].cpu(), rows[:, H * D :]), "the key columns of the row must stay as projected"
+    kc, vc = k_cache.view(-1, G, D).double().cpu().numpy(), v_cache.view(-1, G, D).double().cpu().numpy()
+    written = np.zeros(pages * P, bool)
+    for t, slot in enumerate(slots.tolist()):
+        if slot < 0:
+            continue
+        written[slot] = True
+        close(torch.from_numpy(kc[slot]), k_want[t], dtype, f"rotated keys of token {t}")
+        assert np.array_equal(vc[slot], k[t]), f"values of token {t} are not its unrotated keys"
+    assert np.all(kc[~written] == 0) and np.all(vc[~written] == 0)
+
+
+@pytest.mark.parametrize("dtype", list(DTYPES))
 @pytest.mark.parametrize("T,H,N,K", [(1, 3, 24, 32), (40, 5, 20, 20), (9, 2, 80, 128), (70, 4, 48, 192)])
 def test_per_head_product_with_a_gate_per_output(dtype, T, H, N, K):
     from velox_b200.ops import kernels
